@@ -1,0 +1,168 @@
+/* b200attn -- C ABI of the B200 (sm_100a) attention library.
+ *
+ * Every entry point takes plain pointers and sizes (no torch types), launches
+ * asynchronously on the given CUDA stream, never allocates device memory and
+ * never throws: it returns 0 or a negative b200attn_status.  All pointers are
+ * device pointers that stay owned by the caller and must stay valid until the
+ * stream has run the launch.  Strides are in ELEMENTS of the tensor's dtype;
+ * the innermost (head_dim) stride is always 1.
+ *
+ * Each function names the reference interface (rookie-joe/TritonOps,
+ * path:line inside that project) it stands in for.
+ */
+#ifndef B200ATTN_H_
+#define B200ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200ATTN_ABI_VERSION 1
+
+typedef struct CUstream_st* b200attn_stream_t; /* == cudaStream_t */
+
+typedef enum {
+  B200ATTN_OK = 0,
+  B200ATTN_ERR_NULL = -1,        /* a required pointer is NULL */
+  B200ATTN_ERR_DTYPE = -2,       /* dtype is not F16 / BF16 */
+  B200ATTN_ERR_HEAD_DIM = -3,    /* head_dim not in {32, 64, 96, 128} */
+  B200ATTN_ERR_GQA = -4,         /* heads_q not a positive multiple of heads_kv */
+  B200ATTN_ERR_ALIGN = -5,       /* base pointer not 16-byte aligned */
+  B200ATTN_ERR_STRIDE = -6,      /* a stride is not a multiple of 8 elements (16 bytes) */
+  B200ATTN_ERR_SHAPE = -7,       /* negative / zero / inconsistent sizes */
+  B200ATTN_ERR_WORKSPACE = -8,   /* workspace missing or too small */
+  B200ATTN_ERR_MODE = -9,        /* unknown sparsity mode or bad window / block parameters */
+  B200ATTN_ERR_CUDA = -10,       /* a CUDA call failed (launch, tensor-map encode, ...) */
+  B200ATTN_ERR_TOO_LARGE = -11,  /* problem exceeds a built-in limit */
+  B200ATTN_ERR_DEVICE = -12      /* current device is not compute capability 10.x */
+} b200attn_status;
+
+typedef enum { B200ATTN_F16 = 0, B200ATTN_BF16 = 1 } b200attn_dtype;
+
+typedef enum {
+  B200ATTN_DENSE = 0,       /* every (causally) visible key */
+  B200ATTN_WINDOW = 1,      /* the reference's sparsity: local sliding window + global prefix */
+  B200ATTN_BLOCK_LIST = 2   /* explicit sorted KV-block index lists */
+} b200attn_sparsity;
+
+/* ------------------------------------------------------------------------
+ * Prefill (many query tokens per sequence).
+ *
+ * Logical tensors: q [batch, tokens, heads_q, head_dim], k/v [batch, tokens,
+ * heads_kv, head_dim], o like q, lse fp32 [batch, tokens, heads_q].
+ * Two addressing forms:
+ *   packed varlen (the reference's): cu_seqlens != NULL, int32 [batch+1];
+ *     sequence b owns token rows cu[b]..cu[b+1] of one [total_tokens, heads,
+ *     head_dim] array; *_stride_b is ignored.
+ *   fixed length: cu_seqlens == NULL; every sequence has `seqlen` tokens and
+ *     starts at b * *_stride_b.
+ * Query head h reads KV head h / (heads_q / heads_kv).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse;                 /* nullable */
+  int32_t dtype;              /* b200attn_dtype */
+  int32_t batch, heads_q, heads_kv, head_dim;
+  int32_t seqlen;             /* fixed-length form: tokens per sequence */
+  int32_t max_seqlen;         /* varlen form: upper bound on cu[b+1]-cu[b] (sizes the grid) */
+  int64_t total_tokens;       /* varlen form: rows in the packed arrays */
+  const int32_t* cu_seqlens;  /* nullable, see above */
+  int64_t q_stride_b, q_stride_t, q_stride_h;
+  int64_t k_stride_b, k_stride_t, k_stride_h;
+  int64_t v_stride_b, v_stride_t, v_stride_h;
+  int64_t o_stride_b, o_stride_t, o_stride_h;
+  int64_t lse_stride_b, lse_stride_t, lse_stride_h;
+  float softmax_scale;        /* multiplies q.k before the softmax */
+  int32_t scale_has_log2e;    /* 1: softmax_scale already contains log2(e), as the reference's sm_scale does */
+  int32_t causal;             /* 1: key j visible to query i only if j <= i */
+  int32_t lse_base2;          /* 1: store log2-domain LSE of the log2e-prescaled scores (reference), 0: natural log */
+  /* sparsity (ignored by b200attn_prefill_fwd) */
+  int32_t sparsity;           /* b200attn_sparsity */
+  int32_t window_local;       /* WINDOW: i - j < window_local ... */
+  int32_t window_global;      /* ... or j < window_global */
+  const int32_t* block_idx;   /* BLOCK_LIST: int32 [batch, heads_q, n_qblocks, max_nnz], ascending, -1 padded */
+  const int32_t* block_cnt;   /* BLOCK_LIST: int32 [batch, heads_q, n_qblocks] */
+  int32_t block_size;         /* BLOCK_LIST: 64 */
+  int32_t n_qblocks;          /* BLOCK_LIST: third extent of block_idx / block_cnt */
+  int32_t max_nnz;            /* BLOCK_LIST: last extent of block_idx */
+  int32_t* status_word;       /* nullable; device int set non-zero if a bounded device-side wait gave up */
+} b200attn_prefill_args;
+
+/* Dense causal / non-causal varlen GQA forward.  Replaces flash_attn_triton_fwd
+ * (flash_attn_triton/flash_attn_triton.py:595-658) and its kernel (:52-180). */
+int b200attn_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream);
+
+/* Window-sparse (local + global) or block-list sparse forward.  Replaces the
+ * launcher body at flash_attn_triton/flash_attn_sparse_attn_triton.py:237-326
+ * and its kernel (:47-234), with the mask of the torch function at :422-433. */
+int b200attn_sparse_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Decoding (one query token per sequence over a padded KV cache).
+ *
+ * q [batch, heads_q, head_dim], k_cache/v_cache [batch, capacity, heads_kv,
+ * head_dim], o like q.  Lengths come from cu_seqlens (len_b = cu[b+1]-cu[b],
+ * exactly the reference's use of it) or from seqlens (int32 [batch]); give
+ * one of the two.  Split-KV: phase 1 writes fp32 partials into `workspace`,
+ * phase 2 combines them by their log-sum-exp.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  void* o;
+  int32_t dtype;
+  int32_t batch, heads_q, heads_kv, head_dim;
+  int32_t max_seqlen;         /* upper bound on the lengths (<= cache capacity) */
+  const int32_t* cu_seqlens;  /* nullable */
+  const int32_t* seqlens;     /* nullable */
+  int64_t q_stride_b, q_stride_h;
+  int64_t k_stride_b, k_stride_t, k_stride_h;
+  int64_t v_stride_b, v_stride_t, v_stride_h;
+  int64_t o_stride_b, o_stride_h;
+  float softmax_scale;        /* natural scale, e.g. head_dim^-0.5 */
+  int32_t chunk_tokens;       /* split size, multiple of 64; 0 = 512 */
+  /* sparsity (ignored by b200attn_decode_fwd) */
+  int32_t sparsity;
+  int32_t window_global;      /* WINDOW: key j visible iff j < window_global ... */
+  int32_t window_local;       /* ... or j >= len - window_local */
+  const int32_t* block_idx;   /* BLOCK_LIST: int32 [batch, heads_kv, max_sel] ascending, -1 padded */
+  const int32_t* block_cnt;   /* BLOCK_LIST: nullable int32 [batch, heads_kv]; NULL = max_sel entries */
+  int32_t block_size;         /* BLOCK_LIST: multiple of 16 */
+  int32_t max_sel;
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status_word;       /* nullable, reserved */
+} b200attn_decode_args;
+
+/* Bytes of scratch b200attn_decode_fwd / b200attn_sparse_decode_fwd need. */
+size_t b200attn_decode_workspace_bytes(const b200attn_decode_args* args);
+
+/* GQA split-KV decoding + LSE combine.  Replaces flash_attention_decoding
+ * (flash_attn_triton/flash_attn_decoding.py:213-336) and its two kernels
+ * (:9-122, :126-210). */
+int b200attn_decode_fwd(const b200attn_decode_args* args, b200attn_stream_t stream);
+
+/* Window (sink + recent) or block-list decoding.  Replaces
+ * flash_attention_sparse_decoding (flash_attn_triton/flash_attn_decoding_sparse.py:222-365)
+ * and its kernels (:10-127, :131-219). */
+int b200attn_sparse_decode_fwd(const b200attn_decode_args* args, b200attn_stream_t stream);
+
+/* Prefill needs no scratch; kept so callers can size buffers uniformly. */
+size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args* args);
+
+const char* b200attn_strerror(int status);
+int b200attn_abi_version(void);
+/* Number of kernels the last call on this thread launched (for accounting). */
+int b200attn_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200ATTN_H_ */

@@ -1,0 +1,106 @@
+"""The C-ABI library builds, loads and exports every symbol include/b200attn.h
+declares; argument validation returns the documented status codes without
+touching a GPU."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from tritonops_b200 import _lib, build
+    build.build_library()
+    return _lib.lib()
+
+
+def declared_functions():
+    src = open(os.path.join(ROOT, "include", "b200attn.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200attn_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_header_symbols_exported(lib):
+    from tritonops_b200 import _lib
+    names = declared_functions()
+    assert "b200attn_prefill_fwd" in names and "b200attn_decode_fwd" in names
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in b200attn.h but not exported"
+        assert n in _lib.SYMBOLS, f"{n} has no ctypes prototype"
+
+
+def test_struct_sizes_match_header(lib):
+    """ctypes mirrors must have the C layout: compile a tiny probe with gcc."""
+    import subprocess
+    import tempfile
+    from tritonops_b200 import _lib
+    with tempfile.TemporaryDirectory() as d:
+        src = os.path.join(d, "p.c")
+        open(src, "w").write(
+            '#include <stdio.h>\n#include <stddef.h>\n#include "b200attn.h"\n'
+            'int main(){printf("%zu %zu %zu %zu\\n", sizeof(b200attn_prefill_args),'
+            ' sizeof(b200attn_decode_args), offsetof(b200attn_prefill_args, status_word),'
+            ' offsetof(b200attn_decode_args, workspace_bytes));return 0;}\n')
+        exe = os.path.join(d, "p")
+        subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), src, "-o", exe])
+        a, b, c, e = map(int, subprocess.check_output([exe]).split())
+    assert a == C.sizeof(_lib.PrefillArgs) and b == C.sizeof(_lib.DecodeArgs)
+    assert c == _lib.PrefillArgs.status_word.offset
+    assert e == _lib.DecodeArgs.workspace_bytes.offset
+
+
+def test_version_and_strerror(lib):
+    assert lib.b200attn_abi_version() == 1
+    assert lib.b200attn_strerror(0) == b"ok"
+    for code in range(-12, 0):
+        assert b"unknown" not in lib.b200attn_strerror(code)
+    assert b"unknown" in lib.b200attn_strerror(-99)
+
+
+def test_decode_validation_codes(lib):
+    from tritonops_b200._lib import DecodeArgs
+    a = DecodeArgs()
+    assert lib.b200attn_decode_fwd(C.byref(a), None) == -1           # NULL pointers
+    a.q = a.k_cache = a.v_cache = a.o = 0x1000
+    a.seqlens = 0x1000
+    a.dtype = 7
+    assert lib.b200attn_decode_fwd(C.byref(a), None) == -2
+    a.dtype, a.head_dim = 1, 48
+    assert lib.b200attn_decode_fwd(C.byref(a), None) == -3
+    a.head_dim, a.batch, a.heads_q, a.heads_kv = 128, 2, 6, 4
+    assert lib.b200attn_decode_fwd(C.byref(a), None) == -4
+    a.heads_kv = 2
+    a.q = 0x1008
+    assert lib.b200attn_decode_fwd(C.byref(a), None) == -5
+    a.q, a.k_stride_t = 0x1000, 100
+    assert lib.b200attn_decode_fwd(C.byref(a), None) == -6
+    a.k_stride_t, a.max_seqlen = 256, 1024
+    assert lib.b200attn_decode_fwd(C.byref(a), None) == -8           # no workspace
+    a.cu_seqlens = 0x1000
+    assert lib.b200attn_decode_fwd(C.byref(a), None) == -1           # both length forms
+    a.cu_seqlens = None
+    a.sparsity = 2
+    assert lib.b200attn_sparse_decode_fwd(C.byref(a), None) == -1    # block list missing
+    a.sparsity = 5
+    assert lib.b200attn_sparse_decode_fwd(C.byref(a), None) == -9
+
+
+def test_decode_workspace_formula(lib):
+    from tritonops_b200._lib import DecodeArgs
+    a = DecodeArgs(batch=64, heads_q=32, heads_kv=8, head_dim=128, max_seqlen=8192)
+    rows = 64 * 32 * 16
+    assert lib.b200attn_decode_workspace_bytes(C.byref(a)) == rows * 128 * 4 + rows * 4
+    a.sparsity, a.window_global, a.window_local = 1, 64, 1024
+    assert lib.b200attn_decode_workspace_bytes(C.byref(a)) == 64 * 32 * 3 * (128 * 4 + 4)
+
+
+def test_ops_reject_cpu_tensors(lib):
+    import torch
+    from tritonops_b200 import ops
+    q = torch.zeros(1, 2, 64, dtype=torch.float16)
+    kv = torch.zeros(1, 8, 2, 64, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.decode(q, kv, kv, seqlens=torch.tensor([8], dtype=torch.int32))

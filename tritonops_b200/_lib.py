@@ -1,0 +1,89 @@
+"""ctypes binding of libb200attn.so (the C ABI declared in include/b200attn.h).
+
+There is no fallback: if the shared library is missing or a call fails, the
+Python layer raises."""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libb200attn.so")
+
+F16, BF16 = 0, 1
+DENSE, WINDOW, BLOCK_LIST = 0, 1, 2
+
+i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
+
+
+class PrefillArgs(C.Structure):
+    _fields_ = [
+        ("q", vp), ("k", vp), ("v", vp), ("o", vp), ("lse", vp),
+        ("dtype", i32), ("batch", i32), ("heads_q", i32), ("heads_kv", i32), ("head_dim", i32),
+        ("seqlen", i32), ("max_seqlen", i32), ("total_tokens", i64), ("cu_seqlens", vp),
+        ("q_stride_b", i64), ("q_stride_t", i64), ("q_stride_h", i64),
+        ("k_stride_b", i64), ("k_stride_t", i64), ("k_stride_h", i64),
+        ("v_stride_b", i64), ("v_stride_t", i64), ("v_stride_h", i64),
+        ("o_stride_b", i64), ("o_stride_t", i64), ("o_stride_h", i64),
+        ("lse_stride_b", i64), ("lse_stride_t", i64), ("lse_stride_h", i64),
+        ("softmax_scale", f32), ("scale_has_log2e", i32), ("causal", i32), ("lse_base2", i32),
+        ("sparsity", i32), ("window_local", i32), ("window_global", i32),
+        ("block_idx", vp), ("block_cnt", vp), ("block_size", i32), ("n_qblocks", i32),
+        ("max_nnz", i32), ("status_word", vp),
+    ]
+
+
+class DecodeArgs(C.Structure):
+    _fields_ = [
+        ("q", vp), ("k_cache", vp), ("v_cache", vp), ("o", vp),
+        ("dtype", i32), ("batch", i32), ("heads_q", i32), ("heads_kv", i32), ("head_dim", i32),
+        ("max_seqlen", i32), ("cu_seqlens", vp), ("seqlens", vp),
+        ("q_stride_b", i64), ("q_stride_h", i64),
+        ("k_stride_b", i64), ("k_stride_t", i64), ("k_stride_h", i64),
+        ("v_stride_b", i64), ("v_stride_t", i64), ("v_stride_h", i64),
+        ("o_stride_b", i64), ("o_stride_h", i64),
+        ("softmax_scale", f32), ("chunk_tokens", i32),
+        ("sparsity", i32), ("window_global", i32), ("window_local", i32),
+        ("block_idx", vp), ("block_cnt", vp), ("block_size", i32), ("max_sel", i32),
+        ("workspace", vp), ("workspace_bytes", C.c_size_t), ("status_word", vp),
+    ]
+
+
+# every symbol include/b200attn.h declares: name -> (restype, argtypes)
+SYMBOLS = {
+    "b200attn_abi_version": (C.c_int, []),
+    "b200attn_last_launch_count": (C.c_int, []),
+    "b200attn_strerror": (C.c_char_p, [C.c_int]),
+    "b200attn_prefill_workspace_bytes": (C.c_size_t, [C.POINTER(PrefillArgs)]),
+    "b200attn_prefill_fwd": (C.c_int, [C.POINTER(PrefillArgs), vp]),
+    "b200attn_sparse_prefill_fwd": (C.c_int, [C.POINTER(PrefillArgs), vp]),
+    "b200attn_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeArgs)]),
+    "b200attn_decode_fwd": (C.c_int, [C.POINTER(DecodeArgs), vp]),
+    "b200attn_sparse_decode_fwd": (C.c_int, [C.POINTER(DecodeArgs), vp]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises if it has not been built (python -m tritonops_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m tritonops_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        if handle.b200attn_abi_version() != 1:
+            raise RuntimeError("libb200attn.so ABI version mismatch; rebuild it")
+        _lib = handle
+    return _lib
+
+
+def check(status):
+    if status != 0:
+        msg = lib().b200attn_strerror(status).decode()
+        if status in (-8, -10, -12):
+            raise RuntimeError(f"b200attn: {msg} (status {status})")
+        raise ValueError(f"b200attn: {msg} (status {status})")

@@ -1,0 +1,63 @@
+// extern "C" surface of libb200attn.so; declarations and the reference
+// interfaces they replace are in include/b200attn.h.
+#include "common.cuh"
+
+namespace b200attn {
+static thread_local int g_launch_count = 0;
+void set_launch_count(int n) { g_launch_count = n; }
+}  // namespace b200attn
+
+using namespace b200attn;
+
+extern "C" {
+
+int b200attn_abi_version(void) { return B200ATTN_ABI_VERSION; }
+
+int b200attn_last_launch_count(void) { return g_launch_count; }
+
+const char* b200attn_strerror(int status) {
+  switch (status) {
+    case B200ATTN_OK: return "ok";
+    case B200ATTN_ERR_NULL: return "a required pointer is NULL (or both / neither of cu_seqlens and seqlens given)";
+    case B200ATTN_ERR_DTYPE: return "dtype must be fp16 or bf16";
+    case B200ATTN_ERR_HEAD_DIM: return "head_dim must be 32, 64, 96 or 128";
+    case B200ATTN_ERR_GQA: return "heads_q must be a positive multiple of heads_kv";
+    case B200ATTN_ERR_ALIGN: return "base pointer is not 16-byte aligned";
+    case B200ATTN_ERR_STRIDE: return "stride is not a multiple of 8 elements";
+    case B200ATTN_ERR_SHAPE: return "invalid or inconsistent sizes";
+    case B200ATTN_ERR_WORKSPACE: return "workspace missing or too small";
+    case B200ATTN_ERR_MODE: return "bad sparsity mode, window or block-list parameters";
+    case B200ATTN_ERR_CUDA: return "a CUDA call failed";
+    case B200ATTN_ERR_TOO_LARGE: return "problem exceeds a built-in limit";
+    case B200ATTN_ERR_DEVICE: return "device is not compute capability 10.x";
+    default: return "unknown b200attn status";
+  }
+}
+
+size_t b200attn_decode_workspace_bytes(const b200attn_decode_args* args) {
+  return decode_workspace_bytes(args);
+}
+
+int b200attn_decode_fwd(const b200attn_decode_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return decode_fwd(args, false, nullptr, 0, (cudaStream_t)stream);
+}
+
+int b200attn_sparse_decode_fwd(const b200attn_decode_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return decode_fwd(args, true, nullptr, 0, (cudaStream_t)stream);
+}
+
+size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args*) { return 0; }
+
+int b200attn_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return prefill_fwd(args, false, (cudaStream_t)stream);
+}
+
+int b200attn_sparse_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return prefill_fwd(args, true, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,80 @@
+// Shared device / host helpers of the b200attn kernels (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "../../include/b200attn.h"
+
+namespace b200attn {
+
+void set_launch_count(int n);
+
+// implemented in decode.cu / prefill.cu, called by api.cu
+size_t decode_workspace_bytes(const b200attn_decode_args* a);
+int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t scratch_bytes,
+               cudaStream_t stream);
+int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream);
+
+// 16-byte read-only load that does not pollute L1 (data is used once).
+template <typename T>
+__device__ __forceinline__ uint4 ld_nc_16(const T* ptr) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(ptr));
+  return r;
+}
+
+// D(16x8,f32) += A(16x16) * B(16x8), A row-major fragments a0..a3, B column fragments b0,b1.
+template <typename T>
+__device__ __forceinline__ void mma_16816(float* c, unsigned a0, unsigned a1, unsigned a2,
+                                          unsigned a3, unsigned b0, unsigned b1);
+template <>
+__device__ __forceinline__ void mma_16816<__half>(float* c, unsigned a0, unsigned a1, unsigned a2,
+                                                  unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float* c, unsigned a0, unsigned a1,
+                                                         unsigned a2, unsigned a3, unsigned b0,
+                                                         unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// two floats -> one packed 16-bit pair, `lo` in the low half
+template <typename T>
+__device__ __forceinline__ unsigned pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ unsigned pack2<__half>(float lo, float hi) {
+  unsigned r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+template <>
+__device__ __forceinline__ unsigned pack2<__nv_bfloat16>(float lo, float hi) {
+  unsigned r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+template <typename T>
+__device__ __forceinline__ T from_float(float x);
+template <>
+__device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) {
+  return __float2bfloat16_rn(x);
+}
+
+}  // namespace b200attn

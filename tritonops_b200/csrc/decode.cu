@@ -1,0 +1,434 @@
+// Split-KV GQA decoding for sm_100a: one query token per sequence against a
+// padded KV cache, dense / window-sparse / block-list-sparse, plus the
+// log-sum-exp combine.  Stands in for flash_attn_decoding_kernel +
+// flash_attn_decoding_correction_kernel (flash_attn_triton/flash_attn_decoding.py:9-210)
+// and their sparse twins (flash_attn_triton/flash_attn_decoding_sparse.py:10-219).
+//
+// The path is HBM-bound (each K/V byte is used once), so the kernel is built
+// around the memory system: every K and V element goes from global memory
+// straight into registers with 128-bit loads, already in the operand layout
+// of the m16n8k16 tensor-core instruction, so no shared-memory staging and no
+// shuffles sit between the load and the math.  All query heads of one KV head
+// (GQA group, up to 8 per pass) ride in one MMA tile, so the cache is read
+// once per KV head instead of once per query head as the reference does
+// (flash_attn_decoding.py:45).
+//
+//   S^T[g, t] = sum_d Q[g, d] K[t, d]      A = Q (16 x 16, rows >= 8 are zero)
+//                                          B = K^T (16 x 8 tokens)
+//   O^T[d, g] = sum_t V[t, d] P[g, t]      A = V^T (16 d x 16 tokens)
+//                                          B = P^T (16 tokens x 8 heads)
+//
+// The contraction index of the first product (d) and the row index of the
+// second (d again) may be permuted freely, which is what lets a thread feed
+// 8 consecutive d of one token row (one 16-byte load) to the instruction:
+// the C fragment of S^T is, register for register, the B fragment of P^T.
+#include "common.cuh"
+
+namespace b200attn {
+
+constexpr int kDecodeWarps = 4;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kUnit = 16;  // tokens one warp handles per step
+
+struct DecodeParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* part_o;    // [B, Hq, max_chunks, D] fp32, normalised inside the chunk
+  float* part_lse;  // [B, Hq, max_chunks] base-2 LSE of the prescaled scores
+  const int32_t* cu_seqlens;
+  const int32_t* seqlens;
+  const int32_t* block_idx;
+  const int32_t* block_cnt;
+  long long q_sb, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, o_sb, o_sh;
+  int batch, heads_q, heads_kv, group, ggroups;
+  int chunk, max_chunks;
+  int sparsity, win_global, win_local, block_size, max_sel;
+  float scale_log2;
+};
+
+// How many keys sequence b / kv head hk attends to, and where they live.
+// The visible keys are numbered 0..n-1 ("virtual" positions); to_token maps a
+// virtual position to a row of the cache.
+struct KeyMap {
+  int n;       // number of visible keys
+  int len;     // sequence length
+  int mode;
+  int split;   // WINDOW: virtual positions >= split are shifted by `shift`
+  int shift;
+  int bshift;  // BLOCK_LIST: log2(block_size) when a power of two, else -1
+  int bsize;
+  const int32_t* blocks;
+  __device__ __forceinline__ int to_token(int vpos) const {
+    if (mode == 0) return vpos;
+    if (mode == 1) return vpos < split ? vpos : vpos + shift;
+    int bi = vpos / bsize;
+    return blocks[bi] * bsize + (vpos - bi * bsize);
+  }
+};
+
+__device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
+  return p.seqlens ? p.seqlens[b] : p.cu_seqlens[b + 1] - p.cu_seqlens[b];
+}
+
+__device__ __forceinline__ KeyMap make_keymap(const DecodeParams& p, int b, int hk) {
+  KeyMap m;
+  m.len = max(seq_len_of(p, b), 0);
+  m.mode = p.sparsity;
+  m.split = 0; m.shift = 0; m.bsize = 1; m.bshift = 0; m.blocks = nullptr;
+  if (p.sparsity == 0) {
+    m.n = m.len;
+  } else if (p.sparsity == 1) {
+    // keys j < G or j >= len - L  (flash_attn_decoding_sparse.py:82-85)
+    int g = min(p.win_global, m.len);
+    int start2 = max(m.len - p.win_local, g);
+    m.split = g;
+    m.shift = start2 - g;
+    m.n = g + (m.len - start2);
+  } else {
+    m.bsize = p.block_size;
+    m.blocks = p.block_idx + ((long long)b * p.heads_kv + hk) * p.max_sel;
+    int cnt = p.block_cnt ? min(p.block_cnt[b * p.heads_kv + hk], p.max_sel) : p.max_sel;
+    // trailing -1 entries are padding
+    while (cnt > 0 && m.blocks[cnt - 1] < 0) --cnt;
+    m.n = cnt * p.block_size;
+  }
+  return m;
+}
+
+template <int D>
+struct UnitRegs {
+  static constexpr int KC = D / 32;        // 16-byte chunks of a K row per thread
+  static constexpr int DH = (D + 63) / 64;  // 64-wide d groups of a V row
+  uint4 k[2][KC];  // [8-token tile][chunk]
+  uint4 v[4][DH];  // [token slot][d group]
+  unsigned valid;  // bit nt*2+i: key (8nt + 2tig + i) is a real key
+};
+
+template <typename T, int D>
+__device__ __forceinline__ void load_unit(UnitRegs<D>& r, const T* __restrict__ kbase,
+                                          const T* __restrict__ vbase, long long k_st,
+                                          long long v_st, const KeyMap& km, int v0, int v_end,
+                                          int gid, int tig) {
+  constexpr int KC = UnitRegs<D>::KC, DH = UnitRegs<D>::DH;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    int vp = v0 + 8 * nt + gid;
+    bool ok = vp < v_end;
+    int tok = ok ? km.to_token(vp) : 0;
+    ok = ok && tok >= 0 && tok < km.len;
+    const T* row = kbase + (long long)tok * k_st + 8 * tig;
+#pragma unroll
+    for (int c = 0; c < KC; ++c) r.k[nt][c] = ok ? ld_nc_16(row + 32 * c) : zero;
+  }
+  unsigned valid = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    // token slots 2tig, 2tig+1, 2tig+8, 2tig+9 of the 16-token unit
+    int slot = 2 * tig + (j & 1) + 8 * (j >> 1);
+    int vp = v0 + slot;
+    bool ok = vp < v_end;
+    int tok = ok ? km.to_token(vp) : 0;
+    ok = ok && tok >= 0 && tok < km.len;
+    valid |= ok ? (1u << j) : 0u;
+    const T* row = vbase + (long long)tok * v_st + 8 * gid;
+#pragma unroll
+    for (int h = 0; h < DH; ++h) {
+      bool dok = ok && (64 * h + 8 * gid < D);
+      r.v[j][h] = dok ? ld_nc_16(row + 64 * h) : zero;
+    }
+  }
+  r.valid = valid;
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kDecodeThreads)
+decode_split_kernel(const DecodeParams p) {
+  constexpr int KC = UnitRegs<D>::KC, DH = UnitRegs<D>::DH;
+  constexpr int NMT = 4 * DH;  // 16-row d tiles of O^T
+  const int chunk_id = blockIdx.x;
+  const int hk = blockIdx.y / p.ggroups;
+  const int gg = blockIdx.y % p.ggroups;
+  const int b = blockIdx.z;
+  const KeyMap km = make_keymap(p, b, hk);
+  const int c_begin = chunk_id * p.chunk;
+  if (c_begin >= km.n) return;
+  const int c_end = min(km.n, c_begin + p.chunk);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int g_row = gg * 8 + gid;               // query head inside the GQA group owned by this lane's row
+  const bool g_ok = g_row < p.group;
+
+  const T* qrow = (const T*)p.q + (long long)b * p.q_sb + (long long)(hk * p.group + (g_ok ? g_row : 0)) * p.q_sh;
+  const T* kbase = (const T*)p.k + (long long)b * p.k_sb + (long long)hk * p.k_sh;
+  const T* vbase = (const T*)p.v + (long long)b * p.v_sb + (long long)hk * p.v_sh;
+
+  // Q fragments: chunk c holds d = 32c + 8tig .. +8 of head g_row
+  uint4 qf[KC];
+#pragma unroll
+  for (int c = 0; c < KC; ++c)
+    qf[c] = g_ok ? ld_nc_16(qrow + 32 * c + 8 * tig) : make_uint4(0, 0, 0, 0);
+
+  float acc[NMT][4];
+#pragma unroll
+  for (int i = 0; i < NMT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  float m_run = -INFINITY;  // running max of row gid (base-2 domain), uniform across the quad
+  float l_run = 0.f;        // this thread's share of the row sum
+
+  auto compute = [&](const UnitRegs<D>& r, int v0) {
+    // ---- scores S^T for two 8-token tiles
+    float s[2][2];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ch = 0; ch < KC; ++ch) {
+        mma_16816<T>(c, qf[ch].x, 0u, qf[ch].y, 0u, r.k[nt][ch].x, r.k[nt][ch].y);
+        mma_16816<T>(c, qf[ch].z, 0u, qf[ch].w, 0u, r.k[nt][ch].z, r.k[nt][ch].w);
+      }
+      s[nt][0] = c[0] * p.scale_log2;
+      s[nt][1] = c[1] * p.scale_log2;
+    }
+    // this thread's score columns are token slots 8nt + 2tig + {0,1} == V slots j = 2nt + i
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        if (!((r.valid >> (2 * nt + i)) & 1u)) s[nt][i] = -INFINITY;
+    float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+    const float alpha = exp2f(m_run - m_use);   // m_run = -inf -> 0
+    m_run = m_new;
+    float pr[2][2];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) pr[nt][i] = exp2f(s[nt][i] - m_use);
+    l_run = l_run * alpha + (pr[0][0] + pr[0][1] + pr[1][0] + pr[1][1]);
+    // accumulator columns of this thread are heads 2tig, 2tig+1 -> fetch their factors
+    const float a0 = __shfl_sync(0xffffffffu, alpha, (2 * tig) * 4);
+    const float a1 = __shfl_sync(0xffffffffu, alpha, (2 * tig + 1) * 4);
+    const unsigned pb0 = pack2<T>(pr[0][0], pr[0][1]);
+    const unsigned pb1 = pack2<T>(pr[1][0], pr[1][1]);
+    // ---- O^T += V^T P^T
+#pragma unroll
+    for (int h = 0; h < DH; ++h) {
+      const unsigned* t0 = reinterpret_cast<const unsigned*>(&r.v[0][h]);
+      const unsigned* t1 = reinterpret_cast<const unsigned*>(&r.v[1][h]);
+      const unsigned* t2 = reinterpret_cast<const unsigned*>(&r.v[2][h]);
+      const unsigned* t3 = reinterpret_cast<const unsigned*>(&r.v[3][h]);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        float* c = acc[h * 4 + w];
+        c[0] *= a0; c[1] *= a1; c[2] *= a0; c[3] *= a1;
+        const unsigned ra0 = __byte_perm(t0[w], t1[w], 0x5410);  // d = 8gid+2w,   tokens 2tig, 2tig+1
+        const unsigned ra1 = __byte_perm(t0[w], t1[w], 0x7632);  // d = 8gid+2w+1
+        const unsigned ra2 = __byte_perm(t2[w], t3[w], 0x5410);  // tokens 2tig+8, 2tig+9
+        const unsigned ra3 = __byte_perm(t2[w], t3[w], 0x7632);
+        mma_16816<T>(c, ra0, ra1, ra2, ra3, pb0, pb1);
+      }
+    }
+    (void)v0;
+  };
+
+  // ---- stream the chunk: warps take 16-token units round-robin, loads for
+  // the next unit are in flight while the current one is computed
+  const int stride = kDecodeWarps * kUnit;
+  UnitRegs<D> ra, rb;
+  int u = c_begin + warp * kUnit;
+  if (u < c_end) load_unit<T, D>(ra, kbase, vbase, p.k_st, p.v_st, km, u, c_end, gid, tig);
+  for (; u < c_end; u += 2 * stride) {
+    const bool has_b = u + stride < c_end;
+    if (has_b) load_unit<T, D>(rb, kbase, vbase, p.k_st, p.v_st, km, u + stride, c_end, gid, tig);
+    compute(ra, u);
+    if (u + 2 * stride < c_end)
+      load_unit<T, D>(ra, kbase, vbase, p.k_st, p.v_st, km, u + 2 * stride, c_end, gid, tig);
+    if (has_b) compute(rb, u + stride);
+  }
+
+  // ---- combine the four warps, then write the chunk partial
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  __shared__ float sm_m[kDecodeWarps][8];
+  __shared__ float sm_l[kDecodeWarps][8];
+  __shared__ float sm_o[kDecodeWarps][NMT * 16][8 + 1];
+  if (tig == 0) { sm_m[warp][gid] = m_run; sm_l[warp][gid] = l_run; }
+#pragma unroll
+  for (int mt = 0; mt < NMT; ++mt) {
+    // row index inside the tile list: d = 64h + 8gid + 2w + {0,1}
+    const int h = mt >> 2, w = mt & 3;
+    const int d0 = 64 * h + 8 * gid + 2 * w;
+    sm_o[warp][d0][2 * tig] = acc[mt][0];
+    sm_o[warp][d0][2 * tig + 1] = acc[mt][1];
+    sm_o[warp][d0 + 1][2 * tig] = acc[mt][2];
+    sm_o[warp][d0 + 1][2 * tig + 1] = acc[mt][3];
+  }
+  __syncthreads();
+  const int heads_here = min(8, p.group - gg * 8);
+  for (int idx = threadIdx.x; idx < heads_here * D; idx += kDecodeThreads) {
+    const int g = idx / D, d = idx - g * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) M = fmaxf(M, sm_m[w][g]);
+    const float Ms = (M == -INFINITY) ? 0.f : M;
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) {
+      const float f = exp2f(sm_m[w][g] - Ms);
+      L += sm_l[w][g] * f;
+      O += sm_o[w][d][g] * f;
+    }
+    const int hq = hk * p.group + gg * 8 + g;
+    const long long row = ((long long)b * p.heads_q + hq) * p.max_chunks + chunk_id;
+    p.part_o[row * D + d] = L > 0.f ? O / L : 0.f;
+    if (d == 0) p.part_lse[row] = L > 0.f ? Ms + log2f(L) : -INFINITY;
+  }
+}
+
+// Phase 2: O = sum_c o_c * 2^(lse_c - lse), lse = log2 sum_c 2^lse_c
+// (flash_attn_decoding.py:173-208).  Sequences without visible keys give 0.
+template <typename T, int D>
+__global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeParams p) {
+  const int hq = blockIdx.x, b = blockIdx.y;
+  const KeyMap km = make_keymap(p, b, hq / p.group);
+  const int nchunk = (km.n + p.chunk - 1) / p.chunk;
+  const long long row0 = ((long long)b * p.heads_q + hq) * p.max_chunks;
+  float M = -INFINITY;
+  for (int c = 0; c < nchunk; ++c) M = fmaxf(M, p.part_lse[row0 + c]);
+  const float Ms = (M == -INFINITY) ? 0.f : M;
+  float L = 0.f;
+  for (int c = 0; c < nchunk; ++c) L += exp2f(p.part_lse[row0 + c] - Ms);
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  T* orow = (T*)p.o + (long long)b * p.o_sb + (long long)hq * p.o_sh;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int c = 0; c < nchunk; ++c)
+      acc += p.part_o[(row0 + c) * D + d] * (exp2f(p.part_lse[row0 + c] - Ms) * inv);
+    orow[d] = from_float<T>(acc);
+  }
+}
+
+// --------------------------------------------------------------------------
+// host side
+// --------------------------------------------------------------------------
+static int decode_max_visible(const b200attn_decode_args* a) {
+  if (a->sparsity == B200ATTN_WINDOW) {
+    long long w = (long long)a->window_global + a->window_local;
+    return (int)(w < a->max_seqlen ? w : a->max_seqlen);
+  }
+  if (a->sparsity == B200ATTN_BLOCK_LIST) return a->max_sel * a->block_size;
+  return a->max_seqlen;
+}
+
+static int decode_chunk(const b200attn_decode_args* a) {
+  return a->chunk_tokens > 0 ? a->chunk_tokens : 512;
+}
+
+size_t decode_workspace_bytes(const b200attn_decode_args* a) {
+  if (!a || a->batch <= 0 || a->heads_q <= 0 || a->head_dim <= 0) return 0;
+  int chunk = decode_chunk(a);
+  long long chunks = (decode_max_visible(a) + chunk - 1) / chunk;
+  if (chunks < 1) chunks = 1;
+  long long rows = (long long)a->batch * a->heads_q * chunks;
+  return (size_t)(rows * a->head_dim * 4 + rows * 4);
+}
+
+static int validate_decode(const b200attn_decode_args* a, bool sparse) {
+  if (!a || !a->q || !a->k_cache || !a->v_cache || !a->o) return B200ATTN_ERR_NULL;
+  if (!a->cu_seqlens == !a->seqlens) return B200ATTN_ERR_NULL;  // exactly one of the two
+  if (a->dtype != B200ATTN_F16 && a->dtype != B200ATTN_BF16) return B200ATTN_ERR_DTYPE;
+  if (a->head_dim != 32 && a->head_dim != 64 && a->head_dim != 96 && a->head_dim != 128)
+    return B200ATTN_ERR_HEAD_DIM;
+  if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0 || a->max_seqlen < 0)
+    return B200ATTN_ERR_SHAPE;
+  if (a->batch > 65535) return B200ATTN_ERR_TOO_LARGE;
+  if (a->heads_q % a->heads_kv != 0) return B200ATTN_ERR_GQA;
+  const void* ptrs[3] = {a->q, a->k_cache, a->v_cache};
+  for (const void* ptr : ptrs)
+    if ((uintptr_t)ptr & 15) return B200ATTN_ERR_ALIGN;
+  if ((uintptr_t)a->o & 1) return B200ATTN_ERR_ALIGN;
+  const long long strides[8] = {a->q_stride_b, a->q_stride_h, a->k_stride_b, a->k_stride_t,
+                                a->k_stride_h, a->v_stride_b, a->v_stride_t, a->v_stride_h};
+  for (long long s : strides)
+    if (s % 8 != 0) return B200ATTN_ERR_STRIDE;
+  int chunk = decode_chunk(a);
+  if (chunk % 64 != 0 || chunk <= 0) return B200ATTN_ERR_SHAPE;
+  int mode = sparse ? a->sparsity : B200ATTN_DENSE;
+  if (mode == B200ATTN_WINDOW) {
+    if (a->window_global < 0 || a->window_local < 0) return B200ATTN_ERR_MODE;
+  } else if (mode == B200ATTN_BLOCK_LIST) {
+    if (!a->block_idx) return B200ATTN_ERR_NULL;
+    if (a->block_size <= 0 || a->block_size % 16 != 0 || a->max_sel <= 0) return B200ATTN_ERR_MODE;
+  } else if (mode != B200ATTN_DENSE) {
+    return B200ATTN_ERR_MODE;
+  }
+  return B200ATTN_OK;
+}
+
+template <typename T, int D>
+static int launch_decode_t(const DecodeParams& p, dim3 g1, dim3 g2, cudaStream_t stream) {
+  decode_split_kernel<T, D><<<g1, kDecodeThreads, 0, stream>>>(p);
+  decode_combine_kernel<T, D><<<g2, 128, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+}
+
+template <typename T>
+static int launch_decode_d(int D, const DecodeParams& p, dim3 g1, dim3 g2, cudaStream_t s) {
+  switch (D) {
+    case 32: return launch_decode_t<T, 32>(p, g1, g2, s);
+    case 64: return launch_decode_t<T, 64>(p, g1, g2, s);
+    case 96: return launch_decode_t<T, 96>(p, g1, g2, s);
+    default: return launch_decode_t<T, 128>(p, g1, g2, s);
+  }
+}
+
+// scratch == nullptr: use the caller's workspace from the args.
+int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t scratch_bytes,
+               cudaStream_t stream) {
+  int st = validate_decode(a, sparse);
+  if (st != B200ATTN_OK) return st;
+  b200attn_decode_args eff = *a;
+  if (!sparse) eff.sparsity = B200ATTN_DENSE;
+  void* ws = scratch ? scratch : a->workspace;
+  size_t ws_bytes = scratch ? scratch_bytes : a->workspace_bytes;
+  size_t need = decode_workspace_bytes(&eff);
+  if (!ws || ws_bytes < need) return scratch ? B200ATTN_ERR_TOO_LARGE : B200ATTN_ERR_WORKSPACE;
+  if ((uintptr_t)ws & 15) return B200ATTN_ERR_ALIGN;
+
+  DecodeParams p;
+  p.q = a->q; p.k = a->k_cache; p.v = a->v_cache; p.o = a->o;
+  p.cu_seqlens = a->cu_seqlens; p.seqlens = a->seqlens;
+  p.block_idx = a->block_idx; p.block_cnt = a->block_cnt;
+  p.q_sb = a->q_stride_b; p.q_sh = a->q_stride_h;
+  p.k_sb = a->k_stride_b; p.k_st = a->k_stride_t; p.k_sh = a->k_stride_h;
+  p.v_sb = a->v_stride_b; p.v_st = a->v_stride_t; p.v_sh = a->v_stride_h;
+  p.o_sb = a->o_stride_b; p.o_sh = a->o_stride_h;
+  p.batch = a->batch; p.heads_q = a->heads_q; p.heads_kv = a->heads_kv;
+  p.group = a->heads_q / a->heads_kv;
+  p.ggroups = (p.group + 7) / 8;
+  p.chunk = decode_chunk(&eff);
+  p.max_chunks = (decode_max_visible(&eff) + p.chunk - 1) / p.chunk;
+  if (p.max_chunks < 1) p.max_chunks = 1;
+  p.sparsity = eff.sparsity;
+  p.win_global = a->window_global; p.win_local = a->window_local;
+  p.block_size = a->block_size; p.max_sel = a->max_sel;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  long long rows = (long long)a->batch * a->heads_q * p.max_chunks;
+  p.part_o = (float*)ws;
+  p.part_lse = p.part_o + rows * a->head_dim;
+  if ((long long)a->heads_kv * p.ggroups > 65535) return B200ATTN_ERR_TOO_LARGE;
+
+  dim3 g1(p.max_chunks, a->heads_kv * p.ggroups, a->batch);
+  dim3 g2(a->heads_q, a->batch);
+  set_launch_count(2);
+  return a->dtype == B200ATTN_F16 ? launch_decode_d<__half>(a->head_dim, p, g1, g2, stream)
+                                  : launch_decode_d<__nv_bfloat16>(a->head_dim, p, g1, g2, stream);
+}
+
+}  // namespace b200attn

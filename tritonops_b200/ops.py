@@ -1,0 +1,199 @@
+"""Tensor-level entry points: torch custom ops ("b200attn::*") whose bodies unpack
+the tensors into the C structs of include/b200attn.h and call the extern "C"
+launchers on the current CUDA stream.  PyTorch only supplies device memory and
+streams here; all arithmetic runs in libb200attn.so.  No CPU or eager fallback
+exists: CPU tensors are rejected."""
+import ctypes as C
+import math
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import BLOCK_LIST, DENSE, WINDOW, DecodeArgs, PrefillArgs
+
+LOG2E = 1.4426950408889634
+_DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+# kernels launched through this module since import (bench accounting)
+launch_counter = 0
+
+
+def _count():
+    global launch_counter
+    launch_counter += _lib.lib().b200attn_last_launch_count()
+
+
+def _stream(t: Tensor):
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("b200attn ops take CUDA tensors only (there is no CPU path)")
+
+
+def _rowmajor16(t: Tensor) -> Tensor:
+    """Keep arbitrary outer strides (the reference passes all strides through,
+    flash_attn_triton.py:633-646) but require unit inner stride and 16-byte
+    addressable rows; copy otherwise."""
+    ok = t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:-1])
+    return t if ok else t.contiguous()
+
+
+def _ptr(t: Optional[Tensor]):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _i32(t: Optional[Tensor], dev) -> Optional[Tensor]:
+    if t is None:
+        return None
+    return t.to(device=dev, dtype=torch.int32).contiguous()
+
+
+# --------------------------------------------------------------------------
+# decoding
+# --------------------------------------------------------------------------
+def decode_workspace_bytes(batch, heads_q, head_dim, max_visible, chunk=0) -> int:
+    a = DecodeArgs(batch=batch, heads_q=heads_q, heads_kv=1, head_dim=head_dim,
+                   max_seqlen=max_visible, chunk_tokens=chunk, sparsity=DENSE)
+    return _lib.lib().b200attn_decode_workspace_bytes(C.byref(a))
+
+
+@torch.library.custom_op("b200attn::decode_fwd", mutates_args=())
+def _decode_op(q: Tensor, k: Tensor, v: Tensor, lens: Tensor, lens_are_cu: bool, max_seqlen: int,
+               scale: float, chunk: int, sparsity: int, window_global: int, window_local: int,
+               block_idx: Optional[Tensor], block_cnt: Optional[Tensor],
+               block_size: int) -> Tensor:
+    _need_cuda(q, k, v, lens, block_idx, block_cnt)
+    if q.dtype not in _DT or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("b200attn: q, k, v must share dtype float16 or bfloat16")
+    q, k, v = _rowmajor16(q), _rowmajor16(k), _rowmajor16(v)
+    B, Hq, D = q.shape
+    Hkv = k.shape[2]
+    o = torch.empty(B, Hq, v.shape[3], device=q.device, dtype=q.dtype)
+    a = DecodeArgs()
+    a.q, a.k_cache, a.v_cache, a.o = _ptr(q), _ptr(k), _ptr(v), _ptr(o)
+    a.dtype, a.batch, a.heads_q, a.heads_kv, a.head_dim = _DT[q.dtype], B, Hq, Hkv, D
+    a.max_seqlen = min(max_seqlen, k.shape[1])
+    if lens_are_cu:
+        a.cu_seqlens = _ptr(lens)
+    else:
+        a.seqlens = _ptr(lens)
+    a.q_stride_b, a.q_stride_h = q.stride(0), q.stride(1)
+    a.k_stride_b, a.k_stride_t, a.k_stride_h = k.stride(0), k.stride(1), k.stride(2)
+    a.v_stride_b, a.v_stride_t, a.v_stride_h = v.stride(0), v.stride(1), v.stride(2)
+    a.o_stride_b, a.o_stride_h = o.stride(0), o.stride(1)
+    a.softmax_scale, a.chunk_tokens, a.sparsity = scale, chunk, sparsity
+    a.window_global, a.window_local = window_global, window_local
+    if block_idx is not None:
+        a.block_idx, a.block_cnt = _ptr(block_idx), _ptr(block_cnt)
+        a.block_size, a.max_sel = block_size, block_idx.shape[-1]
+    L = _lib.lib()
+    need = L.b200attn_decode_workspace_bytes(C.byref(a))
+    ws = torch.empty(max(need, 16), device=q.device, dtype=torch.uint8)
+    a.workspace, a.workspace_bytes = _ptr(ws), ws.numel()
+    fn = L.b200attn_decode_fwd if sparsity == DENSE else L.b200attn_sparse_decode_fwd
+    with torch.cuda.device(q.device):
+        _lib.check(fn(C.byref(a), _stream(q)))
+    _count()
+    return o
+
+
+@_decode_op.register_fake
+def _(q, k, v, lens, lens_are_cu, max_seqlen, scale, chunk, sparsity, window_global,
+      window_local, block_idx, block_cnt, block_size):
+    return q.new_empty(q.shape[0], q.shape[1], v.shape[3])
+
+
+def decode(q, k_cache, v_cache, *, cu_seqlens=None, seqlens=None, max_seqlen=None, scale=None,
+           chunk=0, sparsity=DENSE, window_global=0, window_local=0, block_idx=None,
+           block_cnt=None, block_size=64) -> Tensor:
+    """Split-KV GQA decoding; see b200attn_decode_fwd in include/b200attn.h."""
+    if (cu_seqlens is None) == (seqlens is None):
+        raise ValueError("give exactly one of cu_seqlens and seqlens")
+    lens = _i32(cu_seqlens if cu_seqlens is not None else seqlens, q.device)
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    if max_seqlen is None:
+        max_seqlen = k_cache.shape[1]
+    return _decode_op(q, k_cache, v_cache, lens, cu_seqlens is not None, int(max_seqlen),
+                      float(scale), int(chunk), int(sparsity), int(window_global),
+                      int(window_local), _i32(block_idx, q.device), _i32(block_cnt, q.device),
+                      int(block_size))
+
+
+# --------------------------------------------------------------------------
+# prefill
+# --------------------------------------------------------------------------
+@torch.library.custom_op("b200attn::prefill_fwd", mutates_args=())
+def _prefill_op(q: Tensor, k: Tensor, v: Tensor, cu_seqlens: Optional[Tensor], max_seqlen: int,
+                scale: float, scale_has_log2e: bool, causal: bool, lse_base2: bool, sparsity: int,
+                window_local: int, window_global: int, block_idx: Optional[Tensor],
+                block_cnt: Optional[Tensor], block_size: int) -> Tuple[Tensor, Tensor]:
+    _need_cuda(q, k, v, cu_seqlens, block_idx, block_cnt)
+    if q.dtype not in _DT or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("b200attn: q, k, v must share dtype float16 or bfloat16")
+    q, k, v = _rowmajor16(q), _rowmajor16(k), _rowmajor16(v)
+    Bt, T, Hq, D = q.shape
+    Hkv = k.shape[2]
+    o = torch.empty(Bt, T, Hq, v.shape[3], device=q.device, dtype=q.dtype)
+    lse = torch.empty(Bt, T, Hq, device=q.device, dtype=torch.float32)
+    a = PrefillArgs()
+    a.q, a.k, a.v, a.o, a.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse)
+    a.dtype, a.heads_q, a.heads_kv, a.head_dim = _DT[q.dtype], Hq, Hkv, D
+    if cu_seqlens is not None:
+        a.batch, a.cu_seqlens = cu_seqlens.numel() - 1, _ptr(cu_seqlens)
+        a.max_seqlen, a.total_tokens, a.seqlen = max_seqlen, Bt * T if Bt == 1 else T, 0
+        if Bt != 1:
+            raise ValueError("packed varlen tensors must have a leading dimension of 1")
+    else:
+        a.batch, a.seqlen, a.max_seqlen, a.total_tokens = Bt, T, T, T
+    a.q_stride_b, a.q_stride_t, a.q_stride_h = q.stride(0), q.stride(1), q.stride(2)
+    a.k_stride_b, a.k_stride_t, a.k_stride_h = k.stride(0), k.stride(1), k.stride(2)
+    a.v_stride_b, a.v_stride_t, a.v_stride_h = v.stride(0), v.stride(1), v.stride(2)
+    a.o_stride_b, a.o_stride_t, a.o_stride_h = o.stride(0), o.stride(1), o.stride(2)
+    a.lse_stride_b, a.lse_stride_t, a.lse_stride_h = lse.stride(0), lse.stride(1), lse.stride(2)
+    a.softmax_scale, a.scale_has_log2e = scale, int(scale_has_log2e)
+    a.causal, a.lse_base2, a.sparsity = int(causal), int(lse_base2), sparsity
+    a.window_local, a.window_global = window_local, window_global
+    if block_idx is not None:
+        a.block_idx, a.block_cnt, a.block_size = _ptr(block_idx), _ptr(block_cnt), block_size
+        a.n_qblocks, a.max_nnz = block_idx.shape[2], block_idx.shape[3]
+    L = _lib.lib()
+    fn = L.b200attn_prefill_fwd if sparsity == DENSE else L.b200attn_sparse_prefill_fwd
+    with torch.cuda.device(q.device):
+        _lib.check(fn(C.byref(a), _stream(q)))
+    _count()
+    return o, lse
+
+
+@_prefill_op.register_fake
+def _(q, k, v, cu_seqlens, max_seqlen, scale, scale_has_log2e, causal, lse_base2, sparsity,
+      window_local, window_global, block_idx, block_cnt, block_size):
+    return (q.new_empty(*q.shape[:3], v.shape[3]),
+            q.new_empty(q.shape[:3], dtype=torch.float32))
+
+
+def prefill(q, k, v, *, cu_seqlens=None, max_seqlen=None, scale=None, scale_has_log2e=False,
+            causal=True, lse_base2=False, sparsity=DENSE, window_local=0, window_global=0,
+            block_idx=None, block_cnt=None, block_size=64) -> Tuple[Tensor, Tensor]:
+    """Prefill attention forward -> (o, lse); see b200attn_prefill_fwd in include/b200attn.h.
+
+    q [Bt, T, Hq, D]; with cu_seqlens the tensors are packed ([1, total, H, D])."""
+    cu = _i32(cu_seqlens, q.device)
+    if scale is None:
+        scale, scale_has_log2e = q.shape[-1] ** -0.5, False
+    if max_seqlen is None:
+        if cu is not None:
+            # the one host sync of the reference wrapper (flash_attn_triton.py:621);
+            # pass max_seqlen to avoid it
+            max_seqlen = int((cu[1:] - cu[:-1]).max().item()) if cu.numel() > 1 else 0
+        else:
+            max_seqlen = q.shape[1]
+    return _prefill_op(q, k, v, cu, int(max_seqlen), float(scale), bool(scale_has_log2e),
+                       bool(causal), bool(lse_base2), int(sparsity), int(window_local),
+                       int(window_global), _i32(block_idx, q.device), _i32(block_cnt, q.device),
+                       int(block_size))
