@@ -1,7 +1,514 @@
+// Prefill attention forward for sm_100a: dense causal / non-causal varlen GQA and
+// the reference's window sparsity (local sliding window + global prefix).
+// Stands in for flash_attn_fwd_kernel (flash_attn_triton/flash_attn_triton.py:52-180)
+// and its window twin (flash_attn_triton/flash_attn_sparse_attn_triton.py:47-234).
+//
+// One CTA owns 256 consecutive query rows of one (sequence, query head) as two
+// 128-row tiles and walks the visible KV tiles once for both:
+//
+//   warp 9   TMA producer: Q tiles, then K_0, V_0, K_1, V_1, ... into a ring of
+//            128-byte-swizzled shared-memory stages (mbarrier full/empty pairs)
+//   warp 8   MMA issuer (one thread): S_t = Q_t K_j^T and O_t += P_t V_j with
+//            tcgen05.mma; S, P and O live in tensor memory (TMEM)
+//   warps 0-3 / 4-7   softmax warpgroup of tile 0 / tile 1: one thread per query
+//            row reads its S row from TMEM, keeps the running max and sum in
+//            registers (base-2 exponentials), writes P back over S as packed
+//            16-bit values for the P V product, rescales O in TMEM only when
+//            the row max has grown by more than 2^8, and writes the output.
+//
+// While one warpgroup computes the softmax of its tile the tensor core works on
+// the other tile, so MMA and exponentials overlap.  TMEM columns: S0 [0,128),
+// S1 [128,256), O0 [256,256+D), O1 [384,384+D); P_t aliases the first half of S_t.
+// Every mbarrier wait is bounded; a timeout sets *status_word and the CTA drains.
+#include <type_traits>
+
 #include "common.cuh"
+#include "sm100.cuh"
+
 namespace b200attn {
-int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream) {
-  (void)a; (void)sparse; (void)stream;
-  return B200ATTN_ERR_CUDA;
+using namespace sm100;
+
+constexpr int kMmaWarp = 8;
+constexpr int kLoadWarp = 9;
+constexpr int kPrefillThreads = 320;
+constexpr int kTileM = 128;            // query rows per tile
+constexpr int kPairM = 2 * kTileM;     // query rows per CTA
+constexpr float kLazyRescaleLog2 = 8.f;
+
+struct PrefillParams {
+  void* o;
+  float* lse;
+  const int32_t* cu_seqlens;
+  long long o_sb, o_st, o_sh, lse_sb, lse_st, lse_sh;
+  int batch, heads_q, heads_kv, group, head_dim;
+  int seqlen, n_pairs;
+  int causal, window, win_local, win_global;
+  float scale_log2;
+  int lse_base2;
+  int* status_word;
+};
+
+// The ascending sequence of KV tiles a 256-row query block visits: optionally
+// a global prefix range [0, g_cnt) followed by the local range starting at l_lo.
+struct TileSeq {
+  int n, g_cnt, l_lo;
+  __device__ __forceinline__ int kv(int j) const { return j < g_cnt ? j : l_lo + (j - g_cnt); }
+};
+
+template <int BN>
+__device__ __forceinline__ TileSeq make_seq(const PrefillParams& p, int q0, int len) {
+  TileSeq s;
+  const int q_end = min(len, q0 + kPairM);
+  const int hi = ((p.causal ? q_end : len) + BN - 1) / BN;
+  s.n = hi; s.g_cnt = 0; s.l_lo = 0;
+  if (p.window) {
+    const int lo_tok = max(0, q0 - p.win_local + 1);
+    const int l_lo = min(lo_tok / BN, hi);
+    const int g_hi = (min(p.win_global, q_end) + BN - 1) / BN;
+    if (g_hi < l_lo) { s.g_cnt = g_hi; s.l_lo = l_lo; s.n = g_hi + (hi - l_lo); }
+  }
+  return s;
 }
+
+// Does query tile t (rows q0t .. q0t+127) see anything of KV tile kvt?
+template <int BN>
+__device__ __forceinline__ bool tile_active(const PrefillParams& p, int q0t, int len, int kvt) {
+  if (q0t >= len) return false;
+  const int qlast = min(len, q0t + kTileM) - 1;
+  const int kv0 = kvt * BN, kvl = kv0 + BN - 1;
+  if (p.causal && kv0 > qlast) return false;
+  if (p.window && !(kv0 < p.win_global) && !(kvl > q0t - p.win_local)) return false;
+  return true;
+}
+
+// Is some (query, key) pair of the tile pair masked?  (conservative: may say yes)
+template <int BN>
+__device__ __forceinline__ bool tile_needs_mask(const PrefillParams& p, int q0t, int len, int kvt) {
+  const int kv0 = kvt * BN, kv_end = kv0 + BN;
+  bool full = kv_end <= len;
+  if (p.causal) full = full && (kv_end - 1 <= q0t);
+  if (p.window) full = full && ((kv_end <= p.win_global) || (q0t + kTileM - 1 - kv0 < p.win_local));
+  return !full;
+}
+
+__device__ __forceinline__ bool key_visible(const PrefillParams& p, int i, int j, int len) {
+  bool v = j < len;
+  if (p.causal) v = v && (j <= i);
+  if (p.window) v = v && ((i - j < p.win_local) || (j < p.win_global));
+  return v;
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int DP, int BN, int NSTAGE>
+struct PrefillSmem {
+  static constexpr int kQBytes = kTileM * DP * 2;
+  static constexpr int kQPanel = kTileM * 128;  // one 64-column swizzled panel of Q
+  static constexpr int kStageBytes = BN * DP * 2;
+  static constexpr int kKvPanel = BN * 128;
+  static constexpr int kBarOffset = 2 * kQBytes + NSTAGE * kStageBytes;
+  static constexpr int kNumBars = 2 + 2 * NSTAGE + 6;
+  static constexpr int kBytes = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kAlloc = kBytes + 1024;  // slack to align the base to 1024 bytes
+};
+
+template <typename T, int DP, int BN, int NSTAGE>
+__global__ void __launch_bounds__(kPrefillThreads, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+               const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
+  using L = PrefillSmem<DP, BN, NSTAGE>;
+  constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  constexpr uint32_t kIdescQK = idesc_f16(kFmt, false, kTileM, BN);
+  constexpr uint32_t kIdescPV = idesc_f16(kFmt, true, kTileM, DP);
+  constexpr int kPanels = DP / 64;
+
+  // ---- which 256 query rows: heaviest blocks of a head first, heads contiguous
+  const int pair = p.n_pairs - 1 - (int)(blockIdx.x % p.n_pairs);
+  const int bh = blockIdx.x / p.n_pairs;
+  const int h = bh % p.heads_q, b = bh / p.heads_q;
+  const int hk = h / p.group;
+  int seq_start = 0, len = p.seqlen, bcoord = b;
+  if (p.cu_seqlens) {
+    seq_start = p.cu_seqlens[b];
+    len = p.cu_seqlens[b + 1] - seq_start;
+    bcoord = 0;
+  }
+  const int q0 = pair * kPairM;
+  if (q0 >= len) return;
+  const TileSeq seq = make_seq<BN>(p, q0, len);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sQ = smem_base;
+  const uint32_t sKV = smem_base + 2 * L::kQBytes;
+  const uint32_t bars = smem_base + L::kBarOffset;
+  auto q_full = [&](int t) { return bars + 8 * t; };
+  auto kv_full = [&](int s) { return bars + 8 * (2 + s); };
+  auto kv_empty = [&](int s) { return bars + 8 * (2 + NSTAGE + s); };
+  auto s_full = [&](int t) { return bars + 8 * (2 + 2 * NSTAGE + t); };
+  auto p_full = [&](int t) { return bars + 8 * (4 + 2 * NSTAGE + t); };
+  auto o_full = [&](int t) { return bars + 8 * (6 + 2 * NSTAGE + t); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kBarOffset + L::kNumBars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kBarOffset + L::kNumBars * 8 + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(q_full(t), 1);
+      mbar_init(s_full(t), 1);
+      mbar_init(p_full(t), kTileM);
+      mbar_init(o_full(t), 1);
+    }
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  auto tS = [&](int t) { return tmem + 128u * t; };
+  auto tO = [&](int t) { return tmem + 256u + 128u * t; };
+
+  if (warp == kLoadWarp) {
+    // ================================================================= TMA
+    if (lane == 0) {
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+      for (int t = 0; t < 2; ++t) {
+        if (q0 + kTileM * t >= len) continue;
+        mbar_expect_tx(q_full(t), L::kQBytes);
+        for (int pn = 0; pn < kPanels; ++pn)
+          tma_load_4d(sQ + t * L::kQBytes + pn * L::kQPanel, &tmap_q, q_full(t), 64 * pn,
+                      seq_start + q0 + kTileM * t, h, bcoord);
+      }
+      int cnt = 0;
+      for (int j = 0; j < seq.n; ++j) {
+        const int row = seq_start + seq.kv(j) * BN;
+        for (int which = 0; which < 2; ++which, ++cnt) {
+          const int s = cnt % NSTAGE;
+          const uint32_t ph = (cnt / NSTAGE) & 1;
+          mbar_wait(kv_empty(s), ph ^ 1, abort_flag);
+          mbar_expect_tx(kv_full(s), L::kStageBytes);
+          for (int pn = 0; pn < kPanels; ++pn)
+            tma_load_4d(sKV + s * L::kStageBytes + pn * L::kKvPanel, which ? &tmap_v : &tmap_k,
+                        kv_full(s), 64 * pn, row, hk, bcoord);
+        }
+      }
+      // every issued copy must have landed before the CTA may exit
+      for (int c = max(cnt - NSTAGE, 0); c < cnt; ++c)
+        mbar_wait(kv_full(c % NSTAGE), (c / NSTAGE) & 1, abort_flag);
+    }
+  } else if (warp == kMmaWarp) {
+    // ================================================================= MMA
+    if (lane == 0) {
+      int cnt = 0;
+      int pv_cnt[2] = {0, 0};
+      bool q_ready[2] = {false, false};
+      auto wait_stage = [&]() {
+        const int s = cnt % NSTAGE;
+        mbar_wait(kv_full(s), (cnt / NSTAGE) & 1, abort_flag);
+        tc_fence_after();
+        ++cnt;
+        return s;
+      };
+      auto issue_qk = [&](int t, int s) {
+        if (!q_ready[t]) { mbar_wait(q_full(t), 0, abort_flag); tc_fence_after(); q_ready[t] = true; }
+        const uint32_t a = sQ + t * L::kQBytes, bb = sKV + s * L::kStageBytes;
+#pragma unroll
+        for (int ks = 0; ks < DP / 16; ++ks) {
+          const uint32_t off = (ks / 4) * L::kQPanel + (ks % 4) * 32;
+          const uint32_t offb = (ks / 4) * L::kKvPanel + (ks % 4) * 32;
+          mma_ss(tS(t), smem_desc_sw128(a + off, 16, 1024), smem_desc_sw128(bb + offb, 16, 1024),
+                 kIdescQK, ks > 0);
+        }
+        mma_commit(s_full(t));
+      };
+      auto issue_pv = [&](int t, int s) {
+        mbar_wait(p_full(t), pv_cnt[t] & 1, abort_flag);
+        tc_fence_after();
+        const uint32_t bb = sKV + s * L::kStageBytes;
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks)
+          mma_ts(tO(t), tS(t) + 8u * ks, smem_desc_sw128(bb + ks * 2048, L::kKvPanel, 1024),
+                 kIdescPV, (pv_cnt[t] > 0 || ks > 0) ? 1u : 0u);
+        mma_commit(o_full(t));
+        ++pv_cnt[t];
+      };
+      int sK = wait_stage();
+      for (int t = 0; t < 2; ++t)
+        if (tile_active<BN>(p, q0 + kTileM * t, len, seq.kv(0))) issue_qk(t, sK);
+      mma_commit(kv_empty(sK));
+      for (int j = 0; j < seq.n; ++j) {
+        const int sV = wait_stage();
+        const bool more = j + 1 < seq.n;
+        int sKn = 0;
+        for (int t = 0; t < 2; ++t) {
+          const int q0t = q0 + kTileM * t;
+          if (tile_active<BN>(p, q0t, len, seq.kv(j))) issue_pv(t, sV);
+          if (t == 1) mma_commit(kv_empty(sV));
+          if (more) {
+            if (t == 0) sKn = wait_stage();
+            if (tile_active<BN>(p, q0t, len, seq.kv(j + 1))) issue_qk(t, sKn);
+            if (t == 1) mma_commit(kv_empty(sKn));
+          }
+        }
+      }
+    }
+  } else {
+    // ============================================================= softmax
+    const int t = warp >> 2;                       // query tile of this warpgroup
+    const int row = threadIdx.x & (kTileM - 1);    // row inside the tile == TMEM lane
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const int q0t = q0 + kTileM * t;
+    const int qi = q0t + row;                      // query index inside the sequence
+    const float c = p.scale_log2;
+    float m_run = -INFINITY;  // max the stored P / O are relative to (raw score units)
+    float l_run = 0.f;
+    int items = 0;
+    if (q0t < len) {
+      for (int j = 0; j < seq.n; ++j) {
+        const int kvt = seq.kv(j);
+        if (!tile_active<BN>(p, q0t, len, kvt)) continue;
+        mbar_wait(s_full(t), items & 1, abort_flag);
+        tc_fence_after();
+        uint32_t sr[BN];
+#pragma unroll
+        for (int cc = 0; cc < BN / 32; ++cc) tmem_ld32(tS(t) + lane_off + 32 * cc, &sr[32 * cc]);
+        tmem_wait_ld();
+        if (tile_needs_mask<BN>(p, q0t, len, kvt)) {
+          const int kv0 = kvt * BN;
+#pragma unroll
+          for (int x = 0; x < BN; ++x)
+            if (!key_visible(p, qi, kv0 + x, len)) sr[x] = 0xff800000u;  // -inf
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int x = 0; x < BN; x += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sr[x]));
+          mx1 = fmaxf(mx1, __uint_as_float(sr[x + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sr[x + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(sr[x + 3]));
+        }
+        const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+        // keep the stale max unless it is too far behind (first tile: always take)
+        const bool grow = (items == 0) || ((m_new - m_run) * c > kLazyRescaleLog2) ||
+                          (m_run == -INFINITY && m_new != -INFINITY);
+        const float m_use = grow ? m_new : m_run;
+        const float alpha = (m_use == m_run) ? 1.f : ex2((m_run - m_use) * c);
+        if (items > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          // O_t must hold every product issued so far before it is rescaled
+          mbar_wait(o_full(t), (items - 1) & 1, abort_flag);
+          tc_fence_after();
+#pragma unroll
+          for (int cc = 0; cc < DP / 32; ++cc) {
+            uint32_t orr[32];
+            tmem_ld32(tO(t) + lane_off + 32 * cc, orr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int x = 0; x < 32; ++x) orr[x] = __float_as_uint(__uint_as_float(orr[x]) * alpha);
+            tmem_st32(tO(t) + lane_off + 32 * cc, orr);
+          }
+        }
+        const float mc = (m_use == -INFINITY) ? 0.f : m_use * c;
+        float sum0 = 0.f, sum1 = 0.f;
+        uint32_t pr[BN / 2];
+#pragma unroll
+        for (int x = 0; x < BN / 2; ++x) {
+          const float p0 = ex2(fmaf(__uint_as_float(sr[2 * x]), c, -mc));
+          const float p1 = ex2(fmaf(__uint_as_float(sr[2 * x + 1]), c, -mc));
+          sum0 += p0; sum1 += p1;
+          pr[x] = pack2<T>(p0, p1);
+        }
+#pragma unroll
+        for (int cc = 0; cc < BN / 64; ++cc) tmem_st32(tS(t) + lane_off + 32 * cc, &pr[32 * cc]);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(p_full(t));
+        l_run = l_run * alpha + (sum0 + sum1);
+        m_run = m_use;
+        ++items;
+      }
+      // ------------------------------------------------------- epilogue
+      const bool row_ok = qi < len;
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const long long tok = (long long)seq_start + qi;
+      T* orow = (T*)p.o + (p.cu_seqlens ? 0 : (long long)b * p.o_sb) + tok * p.o_st + (long long)h * p.o_sh;
+      if (items > 0) {
+        mbar_wait(o_full(t), (items - 1) & 1, abort_flag);
+        tc_fence_after();
+      }
+#pragma unroll
+      for (int cc = 0; cc < DP / 32; ++cc) {
+        uint32_t orr[32];
+        if (items > 0) {
+          tmem_ld32(tO(t) + lane_off + 32 * cc, orr);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) orr[x] = 0u;
+        }
+        if (row_ok && 32 * cc < p.head_dim) {
+#pragma unroll
+          for (int x = 0; x < 32; x += 8) {
+            uint4 pk;
+            pk.x = pack2<T>(__uint_as_float(orr[x]) * inv, __uint_as_float(orr[x + 1]) * inv);
+            pk.y = pack2<T>(__uint_as_float(orr[x + 2]) * inv, __uint_as_float(orr[x + 3]) * inv);
+            pk.z = pack2<T>(__uint_as_float(orr[x + 4]) * inv, __uint_as_float(orr[x + 5]) * inv);
+            pk.w = pack2<T>(__uint_as_float(orr[x + 6]) * inv, __uint_as_float(orr[x + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + 32 * cc + x) = pk;
+          }
+        }
+      }
+      if (row_ok && p.lse) {
+        float l2 = (l_run > 0.f) ? m_run * c + log2f(l_run) : -INFINITY;
+        if (!p.lse_base2) l2 *= 0.6931471805599453f;
+        p.lse[(p.cu_seqlens ? 0 : (long long)b * p.lse_sb) + tok * p.lse_st + (long long)h * p.lse_sh] = l2;
+      }
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && p.status_word) atomicExch(p.status_word, 1);
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// --------------------------------------------------------------------------
+// host side
+// --------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return (EncodeTiledFn)f;
+  }();
+  return fn;
+}
+
+// [D, tokens, heads, batch] view of a 16-bit tensor, box = 64 x rows x 1 x 1, 128B swizzle.
+static bool make_tmap(CUtensorMap* m, int dtype, const void* base, int D, long long tokens, int heads,
+                      int batch, long long st, long long sh, long long sb, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)tokens, (cuuint64_t)heads, (cuuint64_t)batch};
+  if (batch <= 1 || sb <= 0) sb = st * tokens;
+  cuuint64_t strides[3] = {(cuuint64_t)st * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(m, dtype == B200ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                   4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static int validate_prefill(const b200attn_prefill_args* a, bool sparse) {
+  if (!a || !a->q || !a->k || !a->v || !a->o) return B200ATTN_ERR_NULL;
+  if (a->dtype != B200ATTN_F16 && a->dtype != B200ATTN_BF16) return B200ATTN_ERR_DTYPE;
+  if (a->head_dim != 32 && a->head_dim != 64 && a->head_dim != 96 && a->head_dim != 128)
+    return B200ATTN_ERR_HEAD_DIM;
+  if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0) return B200ATTN_ERR_SHAPE;
+  if (a->heads_q % a->heads_kv != 0) return B200ATTN_ERR_GQA;
+  if (a->cu_seqlens) {
+    if (a->max_seqlen < 0 || a->total_tokens <= 0) return B200ATTN_ERR_SHAPE;
+  } else if (a->seqlen <= 0) {
+    return B200ATTN_ERR_SHAPE;
+  }
+  const void* ptrs[4] = {a->q, a->k, a->v, a->o};
+  for (const void* ptr : ptrs)
+    if ((uintptr_t)ptr & 15) return B200ATTN_ERR_ALIGN;
+  const long long strides[12] = {a->q_stride_b, a->q_stride_t, a->q_stride_h, a->k_stride_b,
+                                 a->k_stride_t, a->k_stride_h, a->v_stride_b, a->v_stride_t,
+                                 a->v_stride_h, a->o_stride_b, a->o_stride_t, a->o_stride_h};
+  for (long long s : strides)
+    if (s % 8 != 0 || s < 0) return B200ATTN_ERR_STRIDE;
+  if (!(a->softmax_scale > 0.f)) return B200ATTN_ERR_SHAPE;
+  int mode = sparse ? a->sparsity : B200ATTN_DENSE;
+  if (mode == B200ATTN_WINDOW) {
+    if (a->window_local < 0 || a->window_global < 0) return B200ATTN_ERR_MODE;
+  } else if (mode == B200ATTN_BLOCK_LIST) {
+    return B200ATTN_ERR_MODE;  // handled by the block-list kernel when present
+  } else if (mode != B200ATTN_DENSE) {
+    return B200ATTN_ERR_MODE;
+  }
+  return B200ATTN_OK;
+}
+
+template <typename T, int DP>
+static int launch_prefill(const b200attn_prefill_args* a, const PrefillParams& p, cudaStream_t stream) {
+  constexpr int BN = 128;
+  constexpr int NSTAGE = DP == 128 ? 4 : 6;
+  using L = PrefillSmem<DP, BN, NSTAGE>;
+  const long long tokens = a->cu_seqlens ? a->total_tokens : a->seqlen;
+  const int tb = a->cu_seqlens ? 1 : a->batch;
+  CUtensorMap tq, tk, tv;
+  if (!make_tmap(&tq, a->dtype, a->q, a->head_dim, tokens, a->heads_q, tb, a->q_stride_t, a->q_stride_h, a->q_stride_b, kTileM) ||
+      !make_tmap(&tk, a->dtype, a->k, a->head_dim, tokens, a->heads_kv, tb, a->k_stride_t, a->k_stride_h, a->k_stride_b, BN) ||
+      !make_tmap(&tv, a->dtype, a->v, a->head_dim, tokens, a->heads_kv, tb, a->v_stride_t, a->v_stride_h, a->v_stride_b, BN))
+    return B200ATTN_ERR_CUDA;
+  auto kern = prefill_kernel<T, DP, BN, NSTAGE>;
+  static bool attr_set = false;  // per instantiation; setting it twice is harmless
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
+      return B200ATTN_ERR_CUDA;
+    attr_set = true;
+  }
+  const long long blocks = (long long)p.n_pairs * a->heads_q * a->batch;
+  if (blocks <= 0) return B200ATTN_OK;
+  if (blocks > 0x7fffffffLL) return B200ATTN_ERR_TOO_LARGE;
+  kern<<<(unsigned)blocks, kPrefillThreads, L::kAlloc, stream>>>(tq, tk, tv, p);
+  set_launch_count(1);
+  return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+}
+
+int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream) {
+  int st = validate_prefill(a, sparse);
+  if (st != B200ATTN_OK) return st;
+  PrefillParams p;
+  p.o = a->o; p.lse = a->lse; p.cu_seqlens = a->cu_seqlens;
+  p.o_sb = a->o_stride_b; p.o_st = a->o_stride_t; p.o_sh = a->o_stride_h;
+  p.lse_sb = a->lse_stride_b; p.lse_st = a->lse_stride_t; p.lse_sh = a->lse_stride_h;
+  p.batch = a->batch; p.heads_q = a->heads_q; p.heads_kv = a->heads_kv;
+  p.group = a->heads_q / a->heads_kv; p.head_dim = a->head_dim;
+  p.seqlen = a->seqlen;
+  const int maxlen = a->cu_seqlens ? a->max_seqlen : a->seqlen;
+  p.n_pairs = (maxlen + kPairM - 1) / kPairM;
+  const bool window = sparse && a->sparsity == B200ATTN_WINDOW;
+  p.causal = window ? 1 : (a->causal ? 1 : 0);
+  p.window = window ? 1 : 0;
+  p.win_local = window ? (a->window_local > (1 << 30) ? (1 << 30) : a->window_local) : 0;
+  p.win_global = window ? a->window_global : 0;
+  p.scale_log2 = a->softmax_scale * (a->scale_has_log2e ? 1.f : 1.4426950408889634f);
+  p.lse_base2 = a->lse_base2;
+  p.status_word = a->status_word;
+  const bool dp64 = a->head_dim <= 64;
+  if (a->dtype == B200ATTN_F16)
+    return dp64 ? launch_prefill<__half, 64>(a, p, stream) : launch_prefill<__half, 128>(a, p, stream);
+  return dp64 ? launch_prefill<__nv_bfloat16, 64>(a, p, stream)
+              : launch_prefill<__nv_bfloat16, 128>(a, p, stream);
+}
+
 }  // namespace b200attn
