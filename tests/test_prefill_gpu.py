@@ -1,0 +1,198 @@
+"""GPU parity of the prefill path (dense causal / non-causal, window-sparse)
+against the CPU oracle and the reference's recorded outputs.  Tolerances:
+max-abs <= 5e-3 (fp16), <= 2e-2 (bf16) against fp32 math on the same rounded
+inputs; LSE compared in natural log after converting the base-2 form."""
+import math
+
+import pytest
+import torch
+
+from cases import build, load_golden
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.float16: 5e-3, torch.bfloat16: 2e-2}
+LOG2E = orc.LOG2E
+
+
+def _mods():
+    from tritonops_b200 import ops, workloads
+    from tritonops_b200.flash_attn_triton import flash_attn_triton as fa
+    from tritonops_b200.flash_attn_triton import flash_attn_sparse_attn_triton as sp
+    return ops, workloads, fa, sp
+
+
+def maxabs(a, b):
+    return (a.float().cpu() - b.float().cpu()).abs().max().item()
+
+
+def make(lens, hq, hkv, d, dtype, seed=0, dist="randn", scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    T = sum(lens)
+    draw = torch.randn if dist == "randn" else torch.rand
+    q = (draw(1, T, hq, d, generator=g) * scale).to(dtype)
+    k = (draw(1, T, hkv, d, generator=g) * scale).to(dtype)
+    v = draw(1, T, hkv, d, generator=g).to(dtype)
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(torch.tensor(lens), 0)
+    return q, k, v, cu
+
+
+def test_golden_reference_outputs():
+    """The inputs the reference itself was run on (torch path and Triton kernels)."""
+    _, _, fa, sp = _mods()
+    gt, gk = load_golden("golden_torch.npz"), load_golden("golden_triton.npz")
+    for name in ("dense_a", "dense_b", "dense_c"):
+        i = build(name)
+        o = fa.flash_attn_triton.apply(i["q"].cuda(), i["k"].cuda(), i["v"].cuda(), i["cu"].cuda())
+        assert maxabs(o, gt[name]["o"]) <= 2e-2
+    for name in ("cfg1", "dense_ragged_f16"):
+        i = build(name)
+        d = i["q"].shape[-1]
+        o, lse2 = fa.flash_attn_triton_fwd(i["q"].cuda(), i["k"].cuda(), i["v"].cuda(),
+                                           i["cu"].cuda(), d ** -0.5 * LOG2E)
+        assert maxabs(o, gk[name]["o"]) <= 5e-3
+        assert maxabs(lse2, gk[name]["lse2"]) <= 5e-3
+    i = build("cfg1")
+    o = fa.flash_attention(i["q"].cuda(), i["k"].cuda(), i["v"].cuda(), i["cu"].cuda(), causal=False)
+    assert maxabs(o, gt["cfg1"]["o_noncausal"]) <= 5e-3
+    i = build("dense_ragged_f16")
+    for L, G in [(64, 100), (256, 256), (128, 64)]:
+        o, lse2 = sp.flash_attn_sparse_triton(i["q"].cuda(), i["k"].cuda(), i["v"].cuda(),
+                                              i["cu"].cuda(), L, G)
+        assert maxabs(o, gk["dense_ragged_f16"][f"win_o_L{L}_G{G}"]) <= 5e-3
+        assert maxabs(lse2, gk["dense_ragged_f16"][f"win_lse2_L{L}_G{G}"]) <= 5e-3
+    i = build("window_bf16")
+    for L, G in [(128, 0), (64, 100), (200, 256), (1, 0), (64, 128)]:
+        o, _ = sp.flash_attn_sparse_triton(i["q"].cuda(), i["k"].cuda(), i["v"].cuda(),
+                                           i["cu"].cuda(), L, G)
+        assert maxabs(o, gt["window_bf16"][f"o_L{L}_G{G}"]) <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,maxlen,hq,hkv,d", [(3, 128, 2, 2, 96), (2, 256, 8, 4, 128), (4, 512, 4, 1, 64)])
+def test_reference_test_configs(dtype, B, maxlen, hq, hkv, d):
+    """flash_attn_triton.py:1001-1009: random lengths in [1, maxlen], U[0,1) inputs."""
+    _, _, fa, _ = _mods()
+    g = torch.Generator().manual_seed(42 + d)
+    lens = torch.randint(1, maxlen + 1, (B,), generator=g).tolist()
+    q, k, v, cu = make(lens, hq, hkv, d, dtype, seed=d, dist="rand")
+    o = fa.flash_attn_triton.apply(q.cuda(), k.cuda(), v.cuda(), cu.cuda())
+    ref, _ = orc.dense_prefill_exact(q, k, v, cu)
+    assert maxabs(o, ref) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("d", [32, 64, 96, 128])
+def test_ragged_lengths_sweep(causal, d):
+    """Every tile-boundary case: lengths around 1, 128, 256, 384 and beyond."""
+    _, _, fa, _ = _mods()
+    lens = [1, 2, 127, 128, 129, 255, 256, 257, 383, 385, 640, 5]
+    q, k, v, cu = make(lens, 4, 2, d, torch.bfloat16, seed=d)
+    o, lse = fa.flash_attention(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), causal=causal, return_lse=True)
+    ref, rl = orc.dense_prefill_exact(q, k, v, cu, causal=causal)
+    assert maxabs(o, ref) <= 2e-2
+    assert maxabs(lse, rl) <= 1e-3
+
+
+def test_zero_length_sequences_and_fixed_length_form():
+    ops, _, fa, _ = _mods()
+    q, k, v, cu = make([0, 200, 0, 130], 2, 2, 64, torch.float16, seed=2)
+    o = fa.flash_attn_triton.apply(q.cuda(), k.cuda(), v.cuda(), cu.cuda())
+    ref, _ = orc.dense_prefill_exact(q, k, v, cu)
+    assert maxabs(o, ref) <= 5e-3
+    # [B,S,H,D] fixed-length form, with and without cu_seqlens, must agree
+    g = torch.Generator().manual_seed(3)
+    B, S = 3, 300
+    q = torch.randn(B, S, 4, 128, generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn(B, S, 2, 128, generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn(B, S, 2, 128, generator=g).to(torch.bfloat16).cuda()
+    o1 = fa.flash_attention(q, k, v, None, causal=True)
+    cu = (torch.arange(B + 1, dtype=torch.int32) * S).cuda()
+    o2 = fa.flash_attention(q.view(1, B * S, 4, 128), k.view(1, B * S, 2, 128),
+                            v.view(1, B * S, 2, 128), cu, causal=True)
+    assert torch.equal(o1.view(1, B * S, 4, 128), o2)
+    ref, _ = orc.dense_prefill_exact(q.view(1, B * S, 4, 128).cpu(), k.view(1, B * S, 2, 128).cpu(),
+                                     v.view(1, B * S, 2, 128).cpu(), cu.cpu())
+    assert maxabs(o2, ref) <= 2e-2
+
+
+def test_strided_heads_layout():
+    """[B,H,S,D] storage seen through permuted [B,S,H,D] views (arbitrary strides)."""
+    _, _, fa, _ = _mods()
+    g = torch.Generator().manual_seed(4)
+    B, H, S, D = 2, 4, 333, 128
+    qs = torch.randn(B, H, S, D, generator=g).to(torch.bfloat16).cuda()
+    ks = torch.randn(B, H, S, D, generator=g).to(torch.bfloat16).cuda()
+    vs = torch.randn(B, H, S, D, generator=g).to(torch.bfloat16).cuda()
+    o = fa.flash_attention(qs.permute(0, 2, 1, 3), ks.permute(0, 2, 1, 3), vs.permute(0, 2, 1, 3),
+                           None, causal=True)
+    cu = torch.arange(B + 1, dtype=torch.int32) * S
+    pk = lambda t: t.permute(0, 2, 1, 3).reshape(1, B * S, H, D).cpu()
+    ref, _ = orc.dense_prefill_exact(pk(qs), pk(ks), pk(vs), cu)
+    assert maxabs(o.reshape(1, B * S, H, D), ref) <= 2e-2
+
+
+@pytest.mark.parametrize("scale", [10.0, 30.0])
+def test_large_magnitude_scores(scale):
+    """Sharp softmax (scores up to hundreds): the lazy rescale must stay exact."""
+    _, _, fa, _ = _mods()
+    q, k, v, cu = make([700, 300], 2, 1, 64, torch.float16, seed=5, scale=scale)
+    o = fa.flash_attn_triton.apply(q.cuda(), k.cuda(), v.cuda(), cu.cuda())
+    ref, _ = orc.dense_prefill_exact(q, k, v, cu)
+    assert torch.isfinite(o).all()
+    assert maxabs(o, ref) <= 5e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("L,G", [(128, 0), (64, 100), (64, 128), (200, 256), (1, 0), (100, 30),
+                                 (256, 256), (300, 700), (1000, 1), (0, 64), (5000, 0)])
+def test_window_prefill(dtype, L, G):
+    """Oracle semantics of the module's torch function for every (L, G), including
+    those where the reference Triton kernel deviates from it (guard at
+    flash_attn_sparse_attn_triton.py:179)."""
+    _, _, _, sp = _mods()
+    lens = [1500, 129, 700, 1]
+    q, k, v, cu = make(lens, 4, 2, 96, dtype, seed=L + G)
+    o, lse2 = sp.flash_attn_sparse_triton(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), L, G)
+    ref, rl = orc.window_prefill_exact(q, k, v, cu, local=L, glob=G)
+    assert maxabs(o, ref) <= TOL[dtype]
+    fin = torch.isfinite(rl)
+    assert maxabs(lse2.cpu()[fin], rl[fin] * LOG2E) <= 2e-3
+    assert bool((lse2.cpu()[~fin] == -math.inf).all())
+
+
+def test_cfg2_shape_properties():
+    """Full config 2 (B=4,H=32,S=4096,D=128 causal bf16): sampled heads against
+    fp32 math on the device, determinism, and prefix invariance (causal rows do
+    not depend on later tokens)."""
+    ops, wl, fa, _ = _mods()
+    w = wl.cfg2("cuda")
+    o, lse = ops.prefill(w.q, w.k, w.v, cu_seqlens=w.cu_seqlens, max_seqlen=w.max_seqlen)
+    o_again, _ = ops.prefill(w.q, w.k, w.v, cu_seqlens=w.cu_seqlens, max_seqlen=w.max_seqlen)
+    assert torch.equal(o, o_again)
+    S = 4096
+    tril = torch.ones(S, S, dtype=torch.bool, device="cuda").tril()
+    for b, h in [(0, 0), (1, 13), (3, 31)]:
+        sl = slice(b * S, (b + 1) * S)
+        s = (w.q[0, sl, h].float() @ w.k[0, sl, h].float().T) * w.scale
+        s = s.masked_fill(~tril, -math.inf)
+        ref = torch.softmax(s, -1) @ w.v[0, sl, h].float()
+        assert (o[0, sl, h].float() - ref).abs().max().item() <= 2e-2
+        assert (lse[0, sl, h] - torch.logsumexp(s, -1)).abs().max().item() <= 1e-3
+    # prefix invariance: the first 1000 tokens of sequence 2 alone give the same rows
+    sl = slice(2 * S, 2 * S + 1000)
+    cu1 = torch.tensor([0, 1000], dtype=torch.int32, device="cuda")
+    o_pre, _ = ops.prefill(w.q[:, sl].contiguous(), w.k[:, sl].contiguous(), w.v[:, sl].contiguous(),
+                           cu_seqlens=cu1, max_seqlen=1000)
+    assert (o_pre.float() - o[:, sl].float()).abs().max().item() <= 2e-2
+
+
+def test_status_word_stays_clear_and_errors():
+    ops, _, fa, _ = _mods()
+    q, k, v, cu = make([100], 4, 3, 64, torch.float16)
+    with pytest.raises(ValueError):
+        fa.flash_attn_triton.apply(q.cuda(), k.cuda(), v.cuda(), cu.cuda())      # 4 % 3
+    q, k, v, cu = make([100], 2, 2, 48, torch.float16)
+    with pytest.raises(ValueError):
+        fa.flash_attn_triton.apply(q.cuda(), k.cuda(), v.cuda(), cu.cuda())      # head_dim 48
