@@ -43,7 +43,7 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while timing."""
+    """nvidia-smi clocks / throttle reasons sampled every 100 ms while timing."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -55,7 +55,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                 "--format=csv,noheader,nounits", "-lms", "200"],
+                 "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -104,35 +104,32 @@ def time_steps(fn, steps, warmup, stream_sync, barrier):
 
 
 # ----------------------------------------------------------------------------
-def cpu_prefill_sample(seconds_hint=15.0):
+def cpu_prefill_sample(seconds_hint=12.0):
     """The reference's CPU path (flash_attn_torch restated) on a bounded sample of
-    config 2: one 4096-token sequence with as many heads as fit the time hint."""
+    config 2: whole 4096-token, 32-head sequences, repeated until the time hint
+    is used up (at least one)."""
     from oracle import attention_oracle as orc
     from tritonops_b200 import workloads
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    S, D = 4096, 128
+    S, D, H = 4096, 128, 32
     g = torch.Generator().manual_seed(1)
-    heads = 2
-    q = torch.randn(1, S, heads, D, generator=g).to(torch.bfloat16)
-    k = torch.randn(1, S, heads, D, generator=g).to(torch.bfloat16)
-    v = torch.randn(1, S, heads, D, generator=g).to(torch.bfloat16)
+    q = torch.randn(1, S, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, S, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(1, S, H, D, generator=g).to(torch.bfloat16)
     cu = torch.tensor([0, S], dtype=torch.int32)
-    t0 = time.perf_counter()
-    orc.dense_prefill_refpath(q, k, v, cu)
-    probe = time.perf_counter() - t0
-    heads = int(max(2, min(32, (seconds_hint / max(probe, 1e-3)) * 2)))
-    q = torch.randn(1, S, heads, D, generator=g).to(torch.bfloat16)
-    k = torch.randn(1, S, heads, D, generator=g).to(torch.bfloat16)
-    v = torch.randn(1, S, heads, D, generator=g).to(torch.bfloat16)
-    t0 = time.perf_counter()
-    orc.dense_prefill_refpath(q, k, v, cu)
-    dt = time.perf_counter() - t0
-    flops = workloads.causal_flops([S], heads, D)
+    n, t0 = 0, time.perf_counter()
+    while True:
+        orc.dense_prefill_refpath(q, k, v, cu)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds_hint or n >= 64:
+            break
+    flops = workloads.causal_flops([S], H, D) * n
     return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=threads, kind="port",
-                sample=f"1 sequence x {heads} heads of cfg2 (S=4096, D=128, causal bf16), "
+                sample=f"{n} sequence(s) of cfg2 (S=4096, H=32, D=128, causal bf16; the full step has 4), "
                        f"{dt:.1f} s, naive torch attention of flash_attn_triton.py:877-915 restated",
-                seconds=dt, heads=heads)
+                seconds=dt)
 
 
 def run_reference(args, rank, world):
@@ -200,7 +197,6 @@ def run_ours(args, rank, world, local_rank):
     launches = (ops.launch_counter - l0) * args.steps     # kernels of ours per timed region
     sampler.start()
     ms = reduce_max(time_steps(step, args.steps, args.warmup, sync, barrier))
-    clocks = sampler.stop()
     total_flops = w.flops * world
     value = total_flops / ms / 1e9                       # TFLOP/s, whole job
     per_launch_tflops = w.flops / ms / 1e9               # this GPU's kernel (1 launch per step)
@@ -259,6 +255,7 @@ def run_ours(args, rank, world, local_rank):
         del w5
     except Exception as e:
         other["cfg5_block_sparse_decode"] = {"error": repr(e)}
+    clocks = sampler.stop()          # sampled over every timed region above
     torch.cuda.empty_cache()
 
     if rank != 0:
