@@ -154,6 +154,32 @@ int b200attn_decode_fwd(const b200attn_decode_args* args, b200attn_stream_t stre
  * and its kernels (:10-127, :131-219). */
 int b200attn_sparse_decode_fwd(const b200attn_decode_args* args, b200attn_stream_t stream);
 
+/* Dense GQA decoding for callers that cannot allocate.  No counterpart in the
+ * reference (its wrapper allocates three tensors per call,
+ * flash_attn_decoding.py:249-261); this entry point exists for hosts where
+ * nobody may call cudaMalloc when a request arrives: an inference server
+ * that has already handed all free HBM to its KV-cache pool, a real-time loop
+ * that must not hit the implicit device synchronisation of cudaMalloc/cudaFree,
+ * or a plugin running inside another runtime's fixed arena.  Same arguments
+ * and results as b200attn_decode_fwd, except that `workspace` and
+ * `workspace_bytes` are ignored: the split-KV partials go to a fixed array of
+ * B200ATTN_NOALLOC_SCRATCH_BYTES that is part of the library image, so every
+ * GPU that loads the library carries those bytes until the process exits.
+ *   - A problem whose b200attn_decode_workspace_bytes() exceeds that size is
+ *     rejected with B200ATTN_ERR_TOO_LARGE (config 3, B=64 Hq=32 D=128 with
+ *     8192-token caches, needs 16.1 MiB and fits).
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and keeps it; make
+ *     that first call before starting any stream capture.  No call allocates:
+ *     no cudaMalloc, cudaFree or allocating library routine is used.
+ *   - All calls on one device share the array and it keeps the previous
+ *     call's contents.  Nothing in it has to start at zero (every partial a
+ *     call reads was written by that same call), but two calls that overlap
+ *     on the GPU -- different streams, or different host threads -- race on
+ *     it: run them on one stream or order them with events. */
+#define B200ATTN_NOALLOC_SCRATCH_BYTES (32u << 20)
+int b200attn_decode_fwd_noalloc(const b200attn_decode_args* args, b200attn_stream_t stream);
+
 /* Prefill needs no scratch; kept so callers can size buffers uniformly. */
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args* args);
 

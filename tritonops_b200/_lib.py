@@ -58,7 +58,9 @@ SYMBOLS = {
     "b200attn_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeArgs)]),
     "b200attn_decode_fwd": (C.c_int, [C.POINTER(DecodeArgs), vp]),
     "b200attn_sparse_decode_fwd": (C.c_int, [C.POINTER(DecodeArgs), vp]),
+    "b200attn_decode_fwd_noalloc": (C.c_int, [C.POINTER(DecodeArgs), vp]),
 }
+NOALLOC_SCRATCH_BYTES = 32 << 20
 
 _lib = None
 

@@ -48,6 +48,11 @@ int b200attn_sparse_decode_fwd(const b200attn_decode_args* args, b200attn_stream
   return decode_fwd(args, true, nullptr, 0, (cudaStream_t)stream);
 }
 
+int b200attn_decode_fwd_noalloc(const b200attn_decode_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return decode_fwd_noalloc(args, (cudaStream_t)stream);
+}
+
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args*) { return 0; }
 
 int b200attn_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream) {

@@ -17,6 +17,7 @@ size_t decode_workspace_bytes(const b200attn_decode_args* a);
 int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t scratch_bytes,
                cudaStream_t stream);
 int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream);
+int decode_fwd_noalloc(const b200attn_decode_args* a, cudaStream_t stream);
 
 // 16-byte read-only load that does not pollute L1 (data is used once).
 template <typename T>

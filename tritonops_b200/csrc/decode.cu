@@ -22,6 +22,8 @@
 // second (d again) may be permuted freely, which is what lets a thread feed
 // 8 consecutive d of one token row (one 16-byte load) to the instruction:
 // the C fragment of S^T is, register for register, the B fragment of P^T.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200attn {
@@ -429,6 +431,35 @@ int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t
   set_launch_count(2);
   return a->dtype == B200ATTN_F16 ? launch_decode_d<__half>(a->head_dim, p, g1, g2, stream)
                                   : launch_decode_d<__nv_bfloat16>(a->head_dim, p, g1, g2, stream);
+}
+
+// --------------------------------------------------------------------------
+// Decoding without any allocation by anyone: the split-KV partials live in a
+// fixed array that is part of the loaded module instead of a caller workspace.
+// --------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = (size_t)B200ATTN_NOALLOC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int decode_fwd_noalloc(const b200attn_decode_args* a, cudaStream_t stream) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void* dev_ptr[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200ATTN_ERR_CUDA;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!dev_ptr[dev]) {
+      // In host code the array's name only stands for the symbol; the address
+      // the kernels may use has to be asked for, once per device, while that
+      // device is current.
+      void* ptr = nullptr;
+      if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return B200ATTN_ERR_CUDA;
+      dev_ptr[dev] = ptr;
+    }
+    scratch = dev_ptr[dev];
+  }
+  return decode_fwd(a, false, scratch, kStaticScratchBytes, stream);
 }
 
 }  // namespace b200attn
