@@ -184,6 +184,8 @@ def run_ours(args, rank, world, local_rank):
 
     sampler = ClockSampler(local_rank)
     LOG2E = 1.4426950408889634
+    if args.only != "all":
+        return run_single(args, dev, sync, barrier, pk)
 
     # ---------------- headline: config 2, each rank its own 4 sequences (seed 1 + rank)
     w = workloads.dense_causal(4, 32, 4096, 128, 1 + rank, dev, name="cfg2")
@@ -286,12 +288,35 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line))
 
 
+def run_single(args, dev, sync, barrier, pk):
+    """One kernel's loop only (used for ncu captures; prints a short JSON line)."""
+    from tritonops_b200 import ops, workloads
+    if args.only == "prefill":
+        w = workloads.dense_causal(4, 32, 4096, 128, 1, dev, name="cfg2")
+        fn = lambda: ops.prefill(w.q, w.k, w.v, cu_seqlens=w.cu_seqlens, max_seqlen=w.max_seqlen)
+        work, unit, peak = w.flops / 1e9, "TFLOP/s", pk["tflops"]
+    elif args.only == "decode":
+        w = workloads.cfg3(dev)
+        fn = lambda: ops.decode(w.q, w.k_cache, w.v_cache, cu_seqlens=w.cu_seqlens, max_seqlen=w.max_seqlen)
+        work, unit, peak = w.kv_bytes / 1e6, "GB/s", pk["gbs"]
+    else:
+        w = workloads.cfg5(dev)
+        fn = lambda: ops.decode(w.q, w.k_cache, w.v_cache, seqlens=w.seqlens, sparsity=ops.BLOCK_LIST,
+                                block_idx=w.block_idx, block_size=64)
+        work, unit, peak = w.kv_bytes / 1e6, "GB/s", pk["gbs"]
+    ms = time_steps(fn, args.steps, args.warmup, sync, barrier)
+    print(json.dumps({"only": args.only, "ms_per_step": ms, "value": work / ms, "unit": unit,
+                      "frac_of_measured_peak": work / ms / peak}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "sparse_decode"],
+                    help="profiling aid: run one kernel's timed loop and print a short line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
