@@ -30,7 +30,16 @@ using namespace sm100;
 
 constexpr int kMmaWarp = 8;
 constexpr int kLoadWarp = 9;
-constexpr int kPrefillThreads = 320;
+constexpr int kPrefillThreads = 384;        // warps 10, 11 only complete the third warpgroup
+constexpr int kSoftmaxRegs = 216;           // per thread, after setmaxnreg (8 warps)
+constexpr int kOtherRegs = 72;              // MMA / TMA / idle warps
+// setmaxnreg.inc can only take registers that setmaxnreg.dec of the same CTA
+// released, so with R registers per thread at launch the budgets must satisfy
+// 128 (R - kOtherRegs) >= 256 (kSoftmaxRegs - R); R = 168 is what 384 threads
+// per CTA allow.  The launcher refuses to run a build whose R is smaller.
+constexpr int kLaunchRegs = 168;
+static_assert(128 * (kLaunchRegs - kOtherRegs) >= 256 * (kSoftmaxRegs - kLaunchRegs),
+              "setmaxnreg budgets would deadlock");
 constexpr int kTileM = 128;            // query rows per tile
 constexpr int kPairM = 2 * kTileM;     // query rows per CTA
 constexpr float kLazyRescaleLog2 = 8.f;
@@ -102,6 +111,36 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// (d0, d1) = (a0, a1) * (b, b) + (c, c) in one packed instruction
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+  asm("{.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+// (d0, d1) += (a0, a1)
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1) {
+  asm("{.reg .b64 ra, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\t"
+      "add.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;}"
+      : "+f"(d0), "+f"(d1)
+      : "f"(a0), "f"(a1));
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 template <int DP, int BN, int NSTAGE>
@@ -181,7 +220,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   auto tS = [&](int t) { return tmem + 128u * t; };
   auto tO = [&](int t) { return tmem + 256u + 128u * t; };
 
-  if (warp == kLoadWarp) {
+  if (warp >= 8) {
+    // third warpgroup: TMA producer, MMA issuer and two idle warps give registers away
+    setmaxnreg_dec<kOtherRegs>();
+    if (warp == kLoadWarp) {
     // ================================================================= TMA
     if (lane == 0) {
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
@@ -209,7 +251,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       for (int c = max(cnt - NSTAGE, 0); c < cnt; ++c)
         mbar_wait(kv_full(c % NSTAGE), (c / NSTAGE) & 1, abort_flag);
     }
-  } else if (warp == kMmaWarp) {
+    } else if (warp == kMmaWarp) {
     // ================================================================= MMA
     if (lane == 0) {
       int cnt = 0;
@@ -265,8 +307,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
       }
     }
+    }
   } else {
     // ============================================================= softmax
+    setmaxnreg_inc<kSoftmaxRegs>();
     const int t = warp >> 2;                       // query tile of this warpgroup
     const int row = threadIdx.x & (kTileM - 1);    // row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
@@ -294,13 +338,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int x = 0; x < BN; x += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(sr[x]));
-          mx1 = fmaxf(mx1, __uint_as_float(sr[x + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(sr[x + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(sr[x + 3]));
+        for (int x = 0; x < BN; x += 8) {
+          mx0 = fmax3(mx0, __uint_as_float(sr[x]), __uint_as_float(sr[x + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(sr[x + 2]), __uint_as_float(sr[x + 3]));
+          mx2 = fmax3(mx2, __uint_as_float(sr[x + 4]), __uint_as_float(sr[x + 5]));
+          mx3 = fmax3(mx3, __uint_as_float(sr[x + 6]), __uint_as_float(sr[x + 7]));
         }
-        const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+        const float m_new = fmax3(m_run, fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         // keep the stale max unless it is too far behind (first tile: always take)
         const bool grow = (items == 0) || ((m_new - m_run) * c > kLazyRescaleLog2) ||
                           (m_run == -INFINITY && m_new != -INFINITY);
@@ -321,15 +365,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           }
         }
         const float mc = (m_use == -INFINITY) ? 0.f : m_use * c;
-        float sum0 = 0.f, sum1 = 0.f;
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
         uint32_t pr[BN / 2];
+        const float neg_mc = -mc;
 #pragma unroll
-        for (int x = 0; x < BN / 2; ++x) {
-          const float p0 = ex2(fmaf(__uint_as_float(sr[2 * x]), c, -mc));
-          const float p1 = ex2(fmaf(__uint_as_float(sr[2 * x + 1]), c, -mc));
-          sum0 += p0; sum1 += p1;
-          pr[x] = pack2<T>(p0, p1);
+        for (int x = 0; x < BN / 2; x += 2) {
+          float e0, e1, e2, e3;
+          ffma2(e0, e1, __uint_as_float(sr[2 * x]), __uint_as_float(sr[2 * x + 1]), c, neg_mc);
+          ffma2(e2, e3, __uint_as_float(sr[2 * x + 2]), __uint_as_float(sr[2 * x + 3]), c, neg_mc);
+          e0 = ex2(e0); e1 = ex2(e1); e2 = ex2(e2); e3 = ex2(e3);
+          fadd2(sum0, sum1, e0, e1);
+          fadd2(sum2, sum3, e2, e3);
+          pr[x] = pack2<T>(e0, e1);
+          pr[x + 1] = pack2<T>(e2, e3);
         }
+        sum0 += sum2; sum1 += sum3;
 #pragma unroll
         for (int cc = 0; cc < BN / 64; ++cc) tmem_st32(tS(t) + lane_off + 32 * cc, &pr[32 * cc]);
         tmem_wait_st();
@@ -472,6 +522,9 @@ static int launch_prefill(const b200attn_prefill_args* a, const PrefillParams& p
   auto kern = prefill_kernel<T, DP, BN, NSTAGE>;
   static bool attr_set = false;  // per instantiation; setting it twice is harmless
   if (!attr_set) {
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return B200ATTN_ERR_CUDA;
+    if (fa.numRegs < kLaunchRegs) return B200ATTN_ERR_CUDA;  // register hand-over would not balance
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
       return B200ATTN_ERR_CUDA;
     attr_set = true;
