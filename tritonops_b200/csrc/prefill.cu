@@ -100,13 +100,6 @@ __device__ __forceinline__ bool tile_needs_mask(const PrefillParams& p, int q0t,
   return !full;
 }
 
-__device__ __forceinline__ bool key_visible(const PrefillParams& p, int i, int j, int len) {
-  bool v = j < len;
-  if (p.causal) v = v && (j <= i);
-  if (p.window) v = v && ((i - j < p.win_local) || (j < p.win_global));
-  return v;
-}
-
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -331,10 +324,25 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int cc = 0; cc < BN / 32; ++cc) tmem_ld32(tS(t) + lane_off + 32 * cc, &sr[32 * cc]);
         tmem_wait_ld();
         if (tile_needs_mask<BN>(p, q0t, len, kvt)) {
+          // Column x of this tile is visible iff x < lim and (x >= lo or x < gl):
+          // lim from the causal diagonal and the sequence end, lo from the local
+          // window, gl from the global prefix.  Kept to a compare + select per
+          // element: this code runs once or twice per CTA, so its size (cold
+          // instruction fetches) matters more than its issue count.
           const int kv0 = kvt * BN;
+          int lim = len - kv0;
+          if (p.causal) lim = min(lim, qi - kv0 + 1);
+          if (!p.window) {
 #pragma unroll
-          for (int x = 0; x < BN; ++x)
-            if (!key_visible(p, qi, kv0 + x, len)) sr[x] = 0xff800000u;  // -inf
+            for (int x = 0; x < BN; ++x)
+              if (x >= lim) sr[x] = 0xff800000u;  // -inf
+          } else {
+            const int lo = qi - p.win_local + 1 - kv0;
+            const int gl = p.win_global - kv0;
+#pragma unroll
+            for (int x = 0; x < BN; ++x)
+              if (x >= lim || (x < lo && x >= gl)) sr[x] = 0xff800000u;
+          }
         }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
@@ -428,7 +436,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     }
   }
 
-  // ---- teardown
+  // ---- teardown (the single-lane roles above reconverge first)
+  __syncwarp();
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag && p.status_word) atomicExch(p.status_word, 1);
