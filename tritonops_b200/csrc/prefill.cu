@@ -100,6 +100,30 @@ __device__ __forceinline__ bool tile_needs_mask(const PrefillParams& p, int q0t,
   return !full;
 }
 
+#ifdef B200ATTN_TRACE
+// Debug builds only: event trace (event id, SM clock) of one heavy CTA.
+__device__ unsigned int g_trace_n;
+__device__ unsigned long long g_trace[1 << 16];
+__device__ __forceinline__ void trace_ev(int id) {
+  if (blockIdx.x != 16 * 40) return;   // one CTA with the longest KV loop
+  long long c;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(c)::"memory");
+  unsigned int i = atomicAdd(&g_trace_n, 1u);
+  if (i < (1u << 16)) g_trace[i] = ((unsigned long long)id << 48) | ((unsigned long long)c & 0xffffffffffffULL);
+}
+#define TRACE(id) trace_ev(id)
+extern "C" int b200attn_debug_read_trace(unsigned long long* host_out, int count) {
+  unsigned int n = 0;
+  cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(n));
+  cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * count);
+  unsigned int zero = 0;
+  cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));
+  return (int)n;
+}
+#else
+#define TRACE(id) do {} while (0)
+#endif
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -218,14 +242,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     setmaxnreg_dec<kOtherRegs>();
     if (warp == kLoadWarp) {
     // ================================================================= TMA
-    if (lane == 0) {
-      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+    {
+      if (elect_one()) { prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); }
       for (int t = 0; t < 2; ++t) {
         if (q0 + kTileM * t >= len) continue;
-        mbar_expect_tx(q_full(t), L::kQBytes);
-        for (int pn = 0; pn < kPanels; ++pn)
-          tma_load_4d(sQ + t * L::kQBytes + pn * L::kQPanel, &tmap_q, q_full(t), 64 * pn,
-                      seq_start + q0 + kTileM * t, h, bcoord);
+        if (elect_one()) {
+          mbar_expect_tx(q_full(t), L::kQBytes);
+          for (int pn = 0; pn < kPanels; ++pn)
+            tma_load_4d(sQ + t * L::kQBytes + pn * L::kQPanel, &tmap_q, q_full(t), 64 * pn,
+                        seq_start + q0 + kTileM * t, h, bcoord);
+        }
+        __syncwarp();
       }
       int cnt = 0;
       for (int j = 0; j < seq.n; ++j) {
@@ -234,10 +261,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           const int s = cnt % NSTAGE;
           const uint32_t ph = (cnt / NSTAGE) & 1;
           mbar_wait(kv_empty(s), ph ^ 1, abort_flag);
-          mbar_expect_tx(kv_full(s), L::kStageBytes);
-          for (int pn = 0; pn < kPanels; ++pn)
-            tma_load_4d(sKV + s * L::kStageBytes + pn * L::kKvPanel, which ? &tmap_v : &tmap_k,
-                        kv_full(s), 64 * pn, row, hk, bcoord);
+          if (elect_one()) {
+            mbar_expect_tx(kv_full(s), L::kStageBytes);
+            for (int pn = 0; pn < kPanels; ++pn)
+              tma_load_4d(sKV + s * L::kStageBytes + pn * L::kKvPanel, which ? &tmap_v : &tmap_k,
+                          kv_full(s), 64 * pn, row, hk, bcoord);
+          }
+          __syncwarp();
         }
       }
       // every issued copy must have landed before the CTA may exit
@@ -246,10 +276,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     }
     } else if (warp == kMmaWarp) {
     // ================================================================= MMA
-    if (lane == 0) {
+    // The whole warp walks the loop in lock step and every lane executes the
+    // (predicated) MMA instructions; only `issue`'s lane really issues them, so
+    // there is no divergent branch and descriptors stay warp-uniform.
+    {
+      const uint32_t issue = elect_one() ? 1u : 0u;
       int cnt = 0;
       int pv_cnt[2] = {0, 0};
       bool q_ready[2] = {false, false};
+      // descriptors of stage 0 / tile 0; other stages and k-steps add to the address field
+      const uint64_t dq0 = smem_desc_sw128(sQ, 16, 1024);
+      const uint64_t dk0 = smem_desc_sw128(sKV, 16, 1024);
+      const uint64_t dv0 = smem_desc_sw128(sKV, L::kKvPanel, 1024);
       auto wait_stage = [&]() {
         const int s = cnt % NSTAGE;
         mbar_wait(kv_full(s), (cnt / NSTAGE) & 1, abort_flag);
@@ -259,31 +297,37 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       };
       auto issue_qk = [&](int t, int s) {
         if (!q_ready[t]) { mbar_wait(q_full(t), 0, abort_flag); tc_fence_after(); q_ready[t] = true; }
-        const uint32_t a = sQ + t * L::kQBytes, bb = sKV + s * L::kStageBytes;
+        const uint64_t da = dq0 + (uint64_t)((t * L::kQBytes) >> 4);
+        const uint64_t db = dk0 + (uint64_t)((s * L::kStageBytes) >> 4);
+#ifndef B200ATTN_NO_QK
 #pragma unroll
-        for (int ks = 0; ks < DP / 16; ++ks) {
-          const uint32_t off = (ks / 4) * L::kQPanel + (ks % 4) * 32;
-          const uint32_t offb = (ks / 4) * L::kKvPanel + (ks % 4) * 32;
-          mma_ss(tS(t), smem_desc_sw128(a + off, 16, 1024), smem_desc_sw128(bb + offb, 16, 1024),
-                 kIdescQK, ks > 0);
-        }
-        mma_commit(s_full(t));
+        for (int ks = 0; ks < DP / 16; ++ks)
+          mma_ss(tS(t), da + (uint64_t)(((ks / 4) * L::kQPanel + (ks % 4) * 32) >> 4),
+                 db + (uint64_t)(((ks / 4) * L::kKvPanel + (ks % 4) * 32) >> 4), kIdescQK, ks > 0, issue);
+#endif
+        mma_commit(s_full(t), issue);
+        if (issue) TRACE(25 + t);
       };
       auto issue_pv = [&](int t, int s) {
         mbar_wait(p_full(t), pv_cnt[t] & 1, abort_flag);
         tc_fence_after();
-        const uint32_t bb = sKV + s * L::kStageBytes;
+        if (issue) TRACE(10 + t);
+        const uint64_t db = dv0 + (uint64_t)((s * L::kStageBytes) >> 4);
+        const uint32_t acc = pv_cnt[t] > 0 ? 1u : 0u;
+#ifndef B200ATTN_NO_PV
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks)
-          mma_ts(tO(t), tS(t) + 8u * ks, smem_desc_sw128(bb + ks * 2048, L::kKvPanel, 1024),
-                 kIdescPV, (pv_cnt[t] > 0 || ks > 0) ? 1u : 0u);
-        mma_commit(o_full(t));
+          mma_ts(tO(t), tS(t) + 8u * ks, db + (uint64_t)((ks * 2048) >> 4), kIdescPV,
+                 ks > 0 ? 1u : acc, issue);
+#endif
+        mma_commit(o_full(t), issue);
+        if (issue) TRACE(20 + t);
         ++pv_cnt[t];
       };
       int sK = wait_stage();
       for (int t = 0; t < 2; ++t)
         if (tile_active<BN>(p, q0 + kTileM * t, len, seq.kv(0))) issue_qk(t, sK);
-      mma_commit(kv_empty(sK));
+      mma_commit(kv_empty(sK), issue);
       for (int j = 0; j < seq.n; ++j) {
         const int sV = wait_stage();
         const bool more = j + 1 < seq.n;
@@ -291,11 +335,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int t = 0; t < 2; ++t) {
           const int q0t = q0 + kTileM * t;
           if (tile_active<BN>(p, q0t, len, seq.kv(j))) issue_pv(t, sV);
-          if (t == 1) mma_commit(kv_empty(sV));
+          if (t == 1) mma_commit(kv_empty(sV), issue);
           if (more) {
             if (t == 0) sKn = wait_stage();
             if (tile_active<BN>(p, q0t, len, seq.kv(j + 1))) issue_qk(t, sKn);
-            if (t == 1) mma_commit(kv_empty(sKn));
+            if (t == 1) mma_commit(kv_empty(sKn), issue);
           }
         }
       }
@@ -319,10 +363,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (!tile_active<BN>(p, q0t, len, kvt)) continue;
         mbar_wait(s_full(t), items & 1, abort_flag);
         tc_fence_after();
+        if (row == 0) TRACE(30 + t);
+#ifdef B200ATTN_SKIP_SOFTMAX   // debug builds: tensor/TMA pipeline alone, results are garbage
+        tc_fence_before();
+        mbar_arrive(p_full(t));
+        ++items;
+        continue;
+#endif
         uint32_t sr[BN];
 #pragma unroll
         for (int cc = 0; cc < BN / 32; ++cc) tmem_ld32(tS(t) + lane_off + 32 * cc, &sr[32 * cc]);
         tmem_wait_ld();
+        if (row == 0) TRACE(40 + t);
         if (tile_needs_mask<BN>(p, q0t, len, kvt)) {
           // Column x of this tile is visible iff x < lim and (x >= lo or x < gl):
           // lim from the causal diagonal and the sequence end, lo from the local
@@ -372,6 +424,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             tmem_st32(tO(t) + lane_off + 32 * cc, orr);
           }
         }
+        if (row == 0) TRACE(50 + t);
         const float mc = (m_use == -INFINITY) ? 0.f : m_use * c;
         float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
         uint32_t pr[BN / 2];
@@ -388,11 +441,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           pr[x + 1] = pack2<T>(e2, e3);
         }
         sum0 += sum2; sum1 += sum3;
+        if (row == 0) TRACE(60 + t);
 #pragma unroll
         for (int cc = 0; cc < BN / 64; ++cc) tmem_st32(tS(t) + lane_off + 32 * cc, &pr[32 * cc]);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(p_full(t));
+        if (row == 0) TRACE(70 + t);
         l_run = l_run * alpha + (sum0 + sum1);
         m_run = m_use;
         ++items;
