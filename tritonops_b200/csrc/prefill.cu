@@ -43,6 +43,7 @@ static_assert(128 * (kLaunchRegs - kOtherRegs) >= 256 * (kSoftmaxRegs - kLaunchR
 constexpr int kTileM = 128;            // query rows per tile
 constexpr int kPairM = 2 * kTileM;     // query rows per CTA
 constexpr float kLazyRescaleLog2 = 8.f;
+constexpr int kHeadGroup = 8;          // (sequence, head) pairs scheduled together
 
 struct PrefillParams {
   void* o;
@@ -182,9 +183,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   constexpr uint32_t kIdescPV = idesc_f16(kFmt, true, kTileM, DP);
   constexpr int kPanels = DP / 64;
 
-  // ---- which 256 query rows: heaviest blocks of a head first, heads contiguous
-  const int pair = p.n_pairs - 1 - (int)(blockIdx.x % p.n_pairs);
-  const int bh = blockIdx.x / p.n_pairs;
+  // ---- which 256 query rows.  (sequence, head) pairs are taken in groups of
+  // kHeadGroup: inside a group the heaviest query blocks of all its heads come
+  // first (longest-first keeps the tail of the launch short), and the group is
+  // small enough that its K/V stay in L2 while its CTAs are resident.
+  const int n_bh = p.batch * p.heads_q;
+  const int per_group = kHeadGroup * p.n_pairs;
+  const int grp = blockIdx.x / per_group;
+  const int in_grp = blockIdx.x - grp * per_group;
+  const int g_heads = min(kHeadGroup, n_bh - grp * kHeadGroup);
+  const int pair = p.n_pairs - 1 - in_grp / g_heads;
+  const int bh = grp * kHeadGroup + in_grp % g_heads;
   const int h = bh % p.heads_q, b = bh / p.heads_q;
   const int hk = h / p.group;
   int seq_start = 0, len = p.seqlen, bcoord = b;
@@ -299,12 +308,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (!q_ready[t]) { mbar_wait(q_full(t), 0, abort_flag); tc_fence_after(); q_ready[t] = true; }
         const uint64_t da = dq0 + (uint64_t)((t * L::kQBytes) >> 4);
         const uint64_t db = dk0 + (uint64_t)((s * L::kStageBytes) >> 4);
-#ifndef B200ATTN_NO_QK
 #pragma unroll
         for (int ks = 0; ks < DP / 16; ++ks)
           mma_ss(tS(t), da + (uint64_t)(((ks / 4) * L::kQPanel + (ks % 4) * 32) >> 4),
                  db + (uint64_t)(((ks / 4) * L::kKvPanel + (ks % 4) * 32) >> 4), kIdescQK, ks > 0, issue);
-#endif
         mma_commit(s_full(t), issue);
         if (issue) TRACE(25 + t);
       };
@@ -314,12 +321,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (issue) TRACE(10 + t);
         const uint64_t db = dv0 + (uint64_t)((s * L::kStageBytes) >> 4);
         const uint32_t acc = pv_cnt[t] > 0 ? 1u : 0u;
-#ifndef B200ATTN_NO_PV
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks)
           mma_ts(tO(t), tS(t) + 8u * ks, db + (uint64_t)((ks * 2048) >> 4), kIdescPV,
                  ks > 0 ? 1u : acc, issue);
-#endif
         mma_commit(o_full(t), issue);
         if (issue) TRACE(20 + t);
         ++pv_cnt[t];
@@ -364,12 +369,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         mbar_wait(s_full(t), items & 1, abort_flag);
         tc_fence_after();
         if (row == 0) TRACE(30 + t);
-#ifdef B200ATTN_SKIP_SOFTMAX   // debug builds: tensor/TMA pipeline alone, results are garbage
-        tc_fence_before();
-        mbar_arrive(p_full(t));
-        ++items;
-        continue;
-#endif
         uint32_t sr[BN];
 #pragma unroll
         for (int cc = 0; cc < BN / 32; ++cc) tmem_ld32(tS(t) + lane_off + 32 * cc, &sr[32 * cc]);
