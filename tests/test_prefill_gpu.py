@@ -196,3 +196,110 @@ def test_status_word_stays_clear_and_errors():
     q, k, v, cu = make([100], 2, 2, 48, torch.float16)
     with pytest.raises(ValueError):
         fa.flash_attn_triton.apply(q.cuda(), k.cuda(), v.cuda(), cu.cuda())      # head_dim 48
+
+
+# ---------------------------------------------------------------- block-list sparsity
+def _random_lists(lens, hq, p_keep, seed, local=2, empty_rows=()):
+    """Per (b, h, q block): the `local` nearest causal blocks plus Bernoulli(p_keep)
+    earlier ones, ascending, -1 padded; `empty_rows` q blocks get an empty list."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(lens)
+    nqb = max((n + 63) // 64 for n in lens)
+    keep = torch.rand(B, hq, nqb, nqb, generator=g) < p_keep
+    i = torch.arange(nqb)[:, None]
+    j = torch.arange(nqb)[None, :]
+    mask = ((keep & (j < i)) | ((j <= i) & (j > i - local)))
+    for qb in empty_rows:
+        mask[:, :, qb, :] = False
+    cnt = mask.sum(-1).to(torch.int32)
+    mx = max(int(cnt.max()), 1)
+    key = torch.where(mask, j.expand_as(mask), torch.full_like(mask, nqb, dtype=torch.long))
+    idx = key.sort(-1).values[..., :mx]
+    idx = torch.where(idx >= nqb, torch.full_like(idx, -1), idx).to(torch.int32)
+    return idx.contiguous(), cnt.contiguous()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("d,hq,hkv", [(128, 4, 2), (64, 2, 2), (96, 4, 1)])
+def test_block_sparse_prefill(dtype, d, hq, hkv):
+    _, _, _, sp = _mods()
+    lens = [300, 1000, 129, 64, 1]
+    q, k, v, cu = make(lens, hq, hkv, d, dtype, seed=d + hq)
+    idx, cnt = _random_lists(lens, hq, 0.3, seed=d, empty_rows=(3,))
+    o, lse = sp.flash_attn_block_sparse(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), idx.cuda(), cnt.cuda())
+    ref, rl = orc.block_sparse_prefill_exact(q, k, v, cu, idx, cnt)
+    assert maxabs(o, ref) <= TOL[dtype]
+    fin = torch.isfinite(rl)
+    assert maxabs(lse.cpu()[fin], rl[fin]) <= 2e-3
+    assert bool((lse.cpu()[~fin] == -math.inf).all())
+    assert o.cpu()[~fin].abs().max().item() == 0.0 if (~fin).any() else True
+
+
+def test_block_sparse_full_lists_equal_dense_and_bad_entries_are_ignored():
+    """All causal blocks listed == dense causal attention; out-of-range, negative
+    and above-diagonal entries are dropped instead of being dereferenced."""
+    _, _, fa, sp = _mods()
+    lens = [500, 257]
+    q, k, v, cu = make(lens, 2, 2, 128, torch.bfloat16, seed=9)
+    nqb = 8
+    idx = torch.arange(nqb, dtype=torch.int32).expand(2, 2, nqb, nqb).contiguous()
+    cnt = (torch.arange(nqb, dtype=torch.int32) + 1).expand(2, 2, nqb).contiguous()
+    o_dense = fa.flash_attention(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), causal=True)
+    o_blk, _ = sp.flash_attn_block_sparse(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), idx.cuda(), cnt.cuda())
+    assert maxabs(o_blk, o_dense) <= 2e-2
+    # same lists plus garbage entries appended
+    idx2 = torch.full((2, 2, nqb, nqb + 3), -1, dtype=torch.int32)
+    idx2[..., :nqb] = idx
+    for qb in range(nqb):
+        idx2[:, :, qb, qb + 1:qb + 4] = torch.tensor([qb + 1, 100000, -7], dtype=torch.int32)
+    cnt2 = cnt + 3
+    o_blk2, _ = sp.flash_attn_block_sparse(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), idx2.cuda(), cnt2.cuda())
+    assert torch.equal(o_blk2, o_blk)
+
+
+def test_block_sparse_window_equivalence():
+    """A block-aligned window written as block lists gives the window result."""
+    _, _, _, sp = _mods()
+    lens = [640, 384]
+    q, k, v, cu = make(lens, 4, 2, 128, torch.bfloat16, seed=21)
+    nqb = 10
+    # keys of the query's own block and the previous one: block lists {qb-1, qb}
+    idx = torch.full((2, 4, nqb, 2), -1, dtype=torch.int32)
+    cnt = torch.zeros(2, 4, nqb, dtype=torch.int32)
+    for qb in range(nqb):
+        row = [x for x in (qb - 1, qb) if x >= 0]
+        idx[:, :, qb, :len(row)] = torch.tensor(row, dtype=torch.int32)
+        cnt[:, :, qb] = len(row)
+    o, _ = sp.flash_attn_block_sparse(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), idx.cuda(), cnt.cuda())
+    ref, _ = orc.block_sparse_prefill_exact(q, k, v, cu, idx, cnt)
+    assert maxabs(o, ref) <= 2e-2
+
+
+def test_cfg4_shape_properties():
+    """Config 4 at full size (B=2,H=16,S=16384,D=128, 64x64 blocks): sampled
+    (b, h) against fp32 dense-masked math on the device, and determinism."""
+    ops, wl, _, sp = _mods()
+    w = wl.cfg4("cuda")
+    f = lambda: sp.flash_attn_block_sparse(w.q, w.k, w.v, w.cu_seqlens, w.block_idx, w.block_cnt,
+                                           max_seqlen=w.max_seqlen)
+    o, lse = f()
+    o2, _ = f()
+    assert torch.equal(o, o2)
+    S, nqb = 16384, 256
+    for b, h in [(0, 0), (1, 11)]:
+        sl = slice(b * S, (b + 1) * S)
+        bm = torch.zeros(nqb, nqb, dtype=torch.bool, device="cuda")
+        row = w.block_idx[b, h]                                   # [nqb, max_nnz]
+        valid = row >= 0
+        qq = torch.arange(nqb, device="cuda")[:, None].expand_as(row)
+        bm[qq[valid], row[valid].long()] = True
+        mask = bm.repeat_interleave(64, 0).repeat_interleave(64, 1)
+        mask &= torch.ones(S, S, dtype=torch.bool, device="cuda").tril()
+        # row chunks keep the fp32 score matrix small
+        for r0 in (0, 8192 - 512, S - 1024):
+            rs = slice(r0, r0 + 1024)
+            s = (w.q[0, sl, h][rs].float() @ w.k[0, sl, h].float().T) * w.scale
+            s = s.masked_fill(~mask[rs], -math.inf)
+            ref = torch.softmax(s, -1) @ w.v[0, sl, h].float()
+            assert (o[0, sl, h][rs].float() - ref).abs().max().item() <= 2e-2
+            assert (lse[0, sl, h][rs] - torch.logsumexp(s, -1)).abs().max().item() <= 1e-3

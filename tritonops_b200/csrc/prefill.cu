@@ -56,7 +56,14 @@ struct PrefillParams {
   float scale_log2;
   int lse_base2;
   int* status_word;
+  // block-list sparsity (block size 64): null block_idx = dense / window
+  const int32_t* block_idx;  // [batch, heads_q, n_qblocks, max_nnz]
+  const int32_t* block_cnt;  // [batch, heads_q, n_qblocks]
+  int n_qblocks, max_nnz;
 };
+
+constexpr int kBlk = 64;              // block-list granularity (tokens)
+constexpr int kMaxBlocks = 2048;      // KV blocks per sequence the merged list can hold
 
 // The ascending sequence of KV tiles a 256-row query block visits: optionally
 // a global prefix range [0, g_cnt) followed by the local range starting at l_lo.
@@ -169,7 +176,12 @@ struct PrefillSmem {
   static constexpr int kKvPanel = BN * 128;
   static constexpr int kBarOffset = 2 * kQBytes + NSTAGE * kStageBytes;
   static constexpr int kNumBars = 2 + 2 * NSTAGE + 6;
-  static constexpr int kBytes = kBarOffset + kNumBars * 8 + 16;
+  // block-list mode: 4 bitmaps (one per 64-row query block of the CTA), then the
+  // merged ascending list of KV blocks with a 4-bit membership mask each
+  static constexpr int kBitmapOffset = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kUlistOffset = kBitmapOffset + 4 * (kMaxBlocks / 32) * 4;
+  static constexpr int kUflagOffset = kUlistOffset + kMaxBlocks * 2;
+  static constexpr int kBytes = kUflagOffset + kMaxBlocks;
   static constexpr int kAlloc = kBytes + 1024;  // slack to align the base to 1024 bytes
 };
 
@@ -246,6 +258,73 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   auto tS = [&](int t) { return tmem + 128u * t; };
   auto tO = [&](int t) { return tmem + 256u + 128u * t; };
 
+  // ---- block-list mode: merge the lists of the CTA's four query blocks into one
+  // ascending list of KV blocks (two blocks form one 128-key step) with a
+  // membership mask per entry.  Entries out of range, or above the diagonal
+  // when causal, are dropped here, so nothing later can index out of bounds.
+  const bool blk = p.block_idx != nullptr;
+  unsigned int* bitmap = reinterpret_cast<unsigned int*>(smem_gen + L::kBitmapOffset);
+  volatile unsigned short* ulist = reinterpret_cast<volatile unsigned short*>(smem_gen + L::kUlistOffset);
+  volatile unsigned char* uflags = reinterpret_cast<volatile unsigned char*>(smem_gen + L::kUflagOffset);
+  volatile int* n_u_slot = reinterpret_cast<volatile int*>(smem_gen + L::kBarOffset + L::kNumBars * 8 + 8);
+  int n_u = 0;
+  if (blk) {
+    constexpr int kWords = kMaxBlocks / 32;
+    for (int i = threadIdx.x; i < 4 * kWords; i += kPrefillThreads) bitmap[i] = 0u;
+    __syncthreads();
+    if (warp < 4) {
+      const int qb = q0 / kBlk + warp;
+      if (qb < p.n_qblocks && qb * kBlk < len) {
+        const long long rowi = ((long long)b * p.heads_q + h) * p.n_qblocks + qb;
+        const int32_t* lst = p.block_idx + rowi * p.max_nnz;
+        const int cnt = min(p.block_cnt[rowi], p.max_nnz);
+        for (int i = lane; i < cnt; i += 32) {
+          const int u = lst[i];
+          if (u >= 0 && u < kMaxBlocks && u * kBlk < len && (!p.causal || u <= qb))
+            atomicOr(&bitmap[warp * kWords + (u >> 5)], 1u << (u & 31));
+        }
+      }
+    }
+    __syncthreads();
+    if (warp == 0) {
+      int base = 0;
+      for (int w0 = 0; w0 < kWords; w0 += 32) {
+        const int w = w0 + lane;
+        const unsigned m0 = bitmap[w], m1 = bitmap[kWords + w], m2 = bitmap[2 * kWords + w],
+                       m3 = bitmap[3 * kWords + w];
+        unsigned any = m0 | m1 | m2 | m3;
+        const int cnt = __popc(any);
+        int incl = cnt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += v;
+        }
+        int pos = base + incl - cnt;
+        while (any) {
+          const int bit = __ffs(any) - 1;
+          any &= any - 1;
+          ulist[pos] = (unsigned short)(w * 32 + bit);
+          uflags[pos] = (unsigned char)(((m0 >> bit) & 1u) | (((m1 >> bit) & 1u) << 1) |
+                                        (((m2 >> bit) & 1u) << 2) | (((m3 >> bit) & 1u) << 3));
+          ++pos;
+        }
+        base += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) *n_u_slot = base;
+    }
+    __syncthreads();
+    n_u = *n_u_slot;
+  }
+  const int n_steps = blk ? (n_u + 1) / 2 : seq.n;
+  // does query tile t take part in step j?
+  auto step_active = [&](int t, int j) -> bool {
+    if (!blk) return tile_active<BN>(p, q0 + kTileM * t, len, seq.kv(j));
+    unsigned f = uflags[2 * j];
+    if (2 * j + 1 < n_u) f |= uflags[2 * j + 1];
+    return (q0 + kTileM * t < len) && ((f >> (2 * t)) & 3u) != 0u;
+  };
+
   if (warp >= 8) {
     // third warpgroup: TMA producer, MMA issuer and two idle warps give registers away
     setmaxnreg_dec<kOtherRegs>();
@@ -264,17 +343,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         __syncwarp();
       }
       int cnt = 0;
-      for (int j = 0; j < seq.n; ++j) {
-        const int row = seq_start + seq.kv(j) * BN;
+      for (int j = 0; j < n_steps; ++j) {
+        // dense / window: one 128-row box; block list: two 64-row boxes (the K/V
+        // tensor maps are then built with 64-row boxes), the second repeating the
+        // first when the list has an odd length (its columns are masked)
+        int row0, row1 = 0;
+        if (blk) {
+          row0 = seq_start + (int)ulist[2 * j] * kBlk;
+          row1 = seq_start + (int)ulist[min(2 * j + 1, n_u - 1)] * kBlk;
+        } else {
+          row0 = seq_start + seq.kv(j) * BN;
+        }
         for (int which = 0; which < 2; ++which, ++cnt) {
           const int s = cnt % NSTAGE;
           const uint32_t ph = (cnt / NSTAGE) & 1;
           mbar_wait(kv_empty(s), ph ^ 1, abort_flag);
           if (elect_one()) {
             mbar_expect_tx(kv_full(s), L::kStageBytes);
-            for (int pn = 0; pn < kPanels; ++pn)
-              tma_load_4d(sKV + s * L::kStageBytes + pn * L::kKvPanel, which ? &tmap_v : &tmap_k,
-                          kv_full(s), 64 * pn, row, hk, bcoord);
+            const CUtensorMap* m = which ? &tmap_v : &tmap_k;
+            for (int pn = 0; pn < kPanels; ++pn) {
+              const uint32_t dst = sKV + s * L::kStageBytes + pn * L::kKvPanel;
+              tma_load_4d(dst, m, kv_full(s), 64 * pn, row0, hk, bcoord);
+              if (blk) tma_load_4d(dst + kBlk * 128, m, kv_full(s), 64 * pn, row1, hk, bcoord);
+            }
           }
           __syncwarp();
         }
@@ -329,21 +420,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (issue) TRACE(20 + t);
         ++pv_cnt[t];
       };
-      int sK = wait_stage();
+      int sK = n_steps > 0 ? wait_stage() : 0;
       for (int t = 0; t < 2; ++t)
-        if (tile_active<BN>(p, q0 + kTileM * t, len, seq.kv(0))) issue_qk(t, sK);
-      mma_commit(kv_empty(sK), issue);
-      for (int j = 0; j < seq.n; ++j) {
+        if (n_steps > 0 && step_active(t, 0)) issue_qk(t, sK);
+      if (n_steps > 0) mma_commit(kv_empty(sK), issue);
+      for (int j = 0; j < n_steps; ++j) {
         const int sV = wait_stage();
-        const bool more = j + 1 < seq.n;
+        const bool more = j + 1 < n_steps;
         int sKn = 0;
         for (int t = 0; t < 2; ++t) {
           const int q0t = q0 + kTileM * t;
-          if (tile_active<BN>(p, q0t, len, seq.kv(j))) issue_pv(t, sV);
+          if (step_active(t, j)) issue_pv(t, sV);
           if (t == 1) mma_commit(kv_empty(sV), issue);
           if (more) {
             if (t == 0) sKn = wait_stage();
-            if (tile_active<BN>(p, q0t, len, seq.kv(j + 1))) issue_qk(t, sKn);
+            if (step_active(t, j + 1)) issue_qk(t, sKn);
             if (t == 1) mma_commit(kv_empty(sKn), issue);
           }
         }
@@ -363,9 +454,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     float l_run = 0.f;
     int items = 0;
     if (q0t < len) {
-      for (int j = 0; j < seq.n; ++j) {
-        const int kvt = seq.kv(j);
-        if (!tile_active<BN>(p, q0t, len, kvt)) continue;
+      for (int j = 0; j < n_steps; ++j) {
+        const int kvt = blk ? 0 : seq.kv(j);
+        if (!step_active(t, j)) continue;
         mbar_wait(s_full(t), items & 1, abort_flag);
         tc_fence_after();
         if (row == 0) TRACE(30 + t);
@@ -374,7 +465,30 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int cc = 0; cc < BN / 32; ++cc) tmem_ld32(tS(t) + lane_off + 32 * cc, &sr[32 * cc]);
         tmem_wait_ld();
         if (row == 0) TRACE(40 + t);
-        if (tile_needs_mask<BN>(p, q0t, len, kvt)) {
+        if (blk) {
+          // columns [0,64) belong to KV block u0, [64,128) to u1; a row sees a
+          // prefix of each half: nothing if its query block does not list the KV
+          // block, else up to the causal diagonal and the sequence end
+          const int u0 = ulist[2 * j];
+          const bool has1 = 2 * j + 1 < n_u;
+          const int u1 = has1 ? (int)ulist[2 * j + 1] : 0;
+          const unsigned f0 = uflags[2 * j], f1 = has1 ? (unsigned)uflags[2 * j + 1] : 0u;
+          const unsigned tile_bits = 3u << (2 * t);
+          bool full = has1 && (f0 & tile_bits) == tile_bits && (f1 & tile_bits) == tile_bits &&
+                      (u1 + 1) * kBlk <= len && (u0 + 1) * kBlk <= len;
+          if (p.causal) full = full && (u1 + 1) * kBlk - 1 <= q0t && (u0 + 1) * kBlk - 1 <= q0t;
+          if (!full) {
+            const int qbl = 2 * t + (row >> 6);
+            int lim0 = ((f0 >> qbl) & 1u) ? min(kBlk, len - u0 * kBlk) : 0;
+            int lim1 = ((f1 >> qbl) & 1u) ? min(kBlk, len - u1 * kBlk) : 0;
+            if (p.causal) { lim0 = min(lim0, qi - u0 * kBlk + 1); lim1 = min(lim1, qi - u1 * kBlk + 1); }
+#pragma unroll
+            for (int x = 0; x < kBlk; ++x) {
+              if (x >= lim0) sr[x] = 0xff800000u;  // -inf
+              if (x >= lim1) sr[kBlk + x] = 0xff800000u;
+            }
+          }
+        } else if (tile_needs_mask<BN>(p, q0t, len, kvt)) {
           // Column x of this tile is visible iff x < lim and (x >= lo or x < gl):
           // lim from the causal diagonal and the sequence end, lo from the local
           // window, gl from the global prefix.  Kept to a compare + select per
@@ -563,7 +677,10 @@ static int validate_prefill(const b200attn_prefill_args* a, bool sparse) {
   if (mode == B200ATTN_WINDOW) {
     if (a->window_local < 0 || a->window_global < 0) return B200ATTN_ERR_MODE;
   } else if (mode == B200ATTN_BLOCK_LIST) {
-    return B200ATTN_ERR_MODE;  // handled by the block-list kernel when present
+    if (!a->block_idx || !a->block_cnt) return B200ATTN_ERR_NULL;
+    if (a->block_size != kBlk || a->n_qblocks <= 0 || a->max_nnz <= 0) return B200ATTN_ERR_MODE;
+    const long long maxlen = a->cu_seqlens ? a->max_seqlen : a->seqlen;
+    if ((maxlen + kBlk - 1) / kBlk > kMaxBlocks) return B200ATTN_ERR_TOO_LARGE;
   } else if (mode != B200ATTN_DENSE) {
     return B200ATTN_ERR_MODE;
   }
@@ -579,8 +696,8 @@ static int launch_prefill(const b200attn_prefill_args* a, const PrefillParams& p
   const int tb = a->cu_seqlens ? 1 : a->batch;
   CUtensorMap tq, tk, tv;
   if (!make_tmap(&tq, a->dtype, a->q, a->head_dim, tokens, a->heads_q, tb, a->q_stride_t, a->q_stride_h, a->q_stride_b, kTileM) ||
-      !make_tmap(&tk, a->dtype, a->k, a->head_dim, tokens, a->heads_kv, tb, a->k_stride_t, a->k_stride_h, a->k_stride_b, BN) ||
-      !make_tmap(&tv, a->dtype, a->v, a->head_dim, tokens, a->heads_kv, tb, a->v_stride_t, a->v_stride_h, a->v_stride_b, BN))
+      !make_tmap(&tk, a->dtype, a->k, a->head_dim, tokens, a->heads_kv, tb, a->k_stride_t, a->k_stride_h, a->k_stride_b, p.block_idx ? kBlk : BN) ||
+      !make_tmap(&tv, a->dtype, a->v, a->head_dim, tokens, a->heads_kv, tb, a->v_stride_t, a->v_stride_h, a->v_stride_b, p.block_idx ? kBlk : BN))
     return B200ATTN_ERR_CUDA;
   auto kern = prefill_kernel<T, DP, BN, NSTAGE>;
   static bool attr_set = false;  // per instantiation; setting it twice is harmless
@@ -620,6 +737,10 @@ int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream
   p.scale_log2 = a->softmax_scale * (a->scale_has_log2e ? 1.f : 1.4426950408889634f);
   p.lse_base2 = a->lse_base2;
   p.status_word = a->status_word;
+  const bool lists = sparse && a->sparsity == B200ATTN_BLOCK_LIST;
+  p.block_idx = lists ? a->block_idx : nullptr;
+  p.block_cnt = lists ? a->block_cnt : nullptr;
+  p.n_qblocks = a->n_qblocks; p.max_nnz = a->max_nnz;
   const bool dp64 = a->head_dim <= 64;
   if (a->dtype == B200ATTN_F16)
     return dp64 ? launch_prefill<__half, 64>(a, p, stream) : launch_prefill<__half, 128>(a, p, stream);
