@@ -240,6 +240,24 @@ def run_ours(args, rank, world, local_rank):
         del w3
     except Exception as e:  # keep the headline even if a secondary config fails
         other["cfg3_gqa_decode"] = {"error": repr(e)}
+    # ---------------- config 4: block-sparse causal prefill (tensor bound, gathered KV blocks)
+    try:
+        from tritonops_b200.flash_attn_triton.flash_attn_sparse_attn_triton import flash_attn_block_sparse
+        w4 = workloads.cfg4(dev)
+        f4 = lambda: flash_attn_block_sparse(w4.q, w4.k, w4.v, w4.cu_seqlens, w4.block_idx, w4.block_cnt,
+                                             max_seqlen=w4.max_seqlen)
+        ms4 = reduce_max(time_steps(f4, max(args.steps, 10), 3, sync, barrier))
+        tf4 = w4.flops / ms4 / 1e9
+        other["cfg4_block_sparse_prefill"] = {
+            "value": tf4 * world, "unit": "TFLOP/s", "ms_per_step": ms4,
+            "roofline": {"bound": "tensor", "achieved": tf4, "peak": pk["tflops"], "unit": "TFLOP/s",
+                         "frac": tf4 / pk["tflops"], "frac_of_nominal_2250": tf4 / 2250.0, "traffic": None},
+            "config": {"workload": "cfg4: block-sparse causal prefill bf16 B=2 H=16 S=16384 D=128, 64x64 "
+                                   "blocks, 8-block window + Bernoulli(0.1) earlier blocks seed 3",
+                       "flops": "4*D per visible (query,key) pair of the listed blocks only"}}
+        del w4
+    except Exception as e:
+        other["cfg4_block_sparse_prefill"] = {"error": repr(e)}
     # ---------------- config 5: top-k block decoding (HBM bound, gathered blocks)
     try:
         w5 = workloads.cfg5(dev)
