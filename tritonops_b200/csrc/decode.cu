@@ -145,8 +145,17 @@ __device__ __forceinline__ void load_unit(UnitRegs<D>& r, const T* __restrict__ 
   r.valid = valid;
 }
 
+#ifndef B200ATTN_DECODE_CTAS
+#define B200ATTN_DECODE_CTAS 4
+#endif
+// Resident CTAs per SM the register budget is sized for.  Four (16 warps)
+// rather than two with a software-pipelined second register buffer: each CTA
+// has a fixed start-up and combine cost of a few microseconds during which it
+// moves no data, and more resident CTAs keep the memory system busy meanwhile.
+constexpr int kDecodeCtasPerSm = B200ATTN_DECODE_CTAS;
+
 template <typename T, int D>
-__global__ void __launch_bounds__(kDecodeThreads)
+__global__ void __launch_bounds__(kDecodeThreads, kDecodeCtasPerSm)
 decode_split_kernel(const DecodeParams p) {
   constexpr int KC = UnitRegs<D>::KC, DH = UnitRegs<D>::DH;
   constexpr int NMT = 4 * DH;  // 16-row d tiles of O^T
@@ -242,16 +251,27 @@ decode_split_kernel(const DecodeParams p) {
   // ---- stream the chunk: warps take 16-token units round-robin, loads for
   // the next unit are in flight while the current one is computed
   const int stride = kDecodeWarps * kUnit;
-  UnitRegs<D> ra, rb;
-  int u = c_begin + warp * kUnit;
-  if (u < c_end) load_unit<T, D>(ra, kbase, vbase, p.k_st, p.v_st, km, u, c_end, gid, tig);
-  for (; u < c_end; u += 2 * stride) {
-    const bool has_b = u + stride < c_end;
-    if (has_b) load_unit<T, D>(rb, kbase, vbase, p.k_st, p.v_st, km, u + stride, c_end, gid, tig);
-    compute(ra, u);
-    if (u + 2 * stride < c_end)
-      load_unit<T, D>(ra, kbase, vbase, p.k_st, p.v_st, km, u + 2 * stride, c_end, gid, tig);
-    if (has_b) compute(rb, u + stride);
+  if (kDecodeCtasPerSm <= 2) {
+    // two register buffers: loads of the next unit in flight during the math
+    UnitRegs<D> ra, rb;
+    int u = c_begin + warp * kUnit;
+    if (u < c_end) load_unit<T, D>(ra, kbase, vbase, p.k_st, p.v_st, km, u, c_end, gid, tig);
+    for (; u < c_end; u += 2 * stride) {
+      const bool has_b = u + stride < c_end;
+      if (has_b) load_unit<T, D>(rb, kbase, vbase, p.k_st, p.v_st, km, u + stride, c_end, gid, tig);
+      compute(ra, u);
+      if (u + 2 * stride < c_end)
+        load_unit<T, D>(ra, kbase, vbase, p.k_st, p.v_st, km, u + 2 * stride, c_end, gid, tig);
+      if (has_b) compute(rb, u + stride);
+    }
+  } else {
+    // one register buffer, more warps per SM: the other warps' loads cover this
+    // warp's math
+    UnitRegs<D> ra;
+    for (int u = c_begin + warp * kUnit; u < c_end; u += stride) {
+      load_unit<T, D>(ra, kbase, vbase, p.k_st, p.v_st, km, u, c_end, gid, tig);
+      compute(ra, u);
+    }
   }
 
   // ---- combine the four warps, then write the chunk partial
