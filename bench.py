@@ -317,6 +317,11 @@ def run_single(args, dev, sync, barrier, pk):
         w = workloads.cfg3(dev)
         fn = lambda: ops.decode(w.q, w.k_cache, w.v_cache, cu_seqlens=w.cu_seqlens, max_seqlen=w.max_seqlen)
         work, unit, peak = w.kv_bytes / 1e6, "GB/s", pk["gbs"]
+    elif args.only == "sparse_prefill":
+        w = workloads.cfg4(dev)
+        fn = lambda: ops.prefill(w.q, w.k, w.v, cu_seqlens=w.cu_seqlens, max_seqlen=w.max_seqlen,
+                                 sparsity=ops.BLOCK_LIST, block_idx=w.block_idx, block_cnt=w.block_cnt)
+        work, unit, peak = w.flops / 1e9, "TFLOP/s", pk["tflops"]
     else:
         w = workloads.cfg5(dev)
         fn = lambda: ops.decode(w.q, w.k_cache, w.v_cache, seqlens=w.seqlens, sparsity=ops.BLOCK_LIST,
@@ -333,7 +338,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "sparse_decode"],
+    ap.add_argument("--only", default="all",
+                    choices=["all", "prefill", "decode", "sparse_prefill", "sparse_decode"],
                     help="profiling aid: run one kernel's timed loop and print a short line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
