@@ -29,6 +29,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "prefill attn TFLOP/s & decode KV HBM GB/s per B200, at 1/2/4/8 GPUs"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
+# ncu captures summarised under profiles/ (same workloads as below)
+TRAFFIC = {"cfg2": 402.877184e6 + 120.129792e6, "cfg3": 1.299476e9 + 9.861120e6,
+           "cfg4": 554.967296e6 + 121.874176e6, "cfg5": 2.148035e9 + 14.810368e6}
 WORKLOAD = "cfg2: dense causal prefill bf16 B=4 H=32 S=4096 D=128 per GPU"
 
 
@@ -233,7 +237,7 @@ def run_ours(args, rank, world, local_rank):
             "value": gbs * world, "unit": "GB/s", "ms_per_step": ms3,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["gbs"], "unit": "GB/s",
                          "frac": gbs / pk["gbs"], "frac_of_nominal_8TBs": gbs / 8000.0,
-                         "traffic": None},
+                         "traffic": TRAFFIC["cfg3"], "algorithmic_bytes": w3.kv_bytes},
             "config": {"workload": "cfg3: GQA decode bf16 B=64 Hq=32 Hkv=8 D=128, cache 8192, "
                                    "len U[1024,8192] seed 2, split chunks 512",
                        "l2": "2.6 GB of KV streamed per step, far larger than L2"}}
@@ -251,7 +255,8 @@ def run_ours(args, rank, world, local_rank):
         other["cfg4_block_sparse_prefill"] = {
             "value": tf4 * world, "unit": "TFLOP/s", "ms_per_step": ms4,
             "roofline": {"bound": "tensor", "achieved": tf4, "peak": pk["tflops"], "unit": "TFLOP/s",
-                         "frac": tf4 / pk["tflops"], "frac_of_nominal_2250": tf4 / 2250.0, "traffic": None},
+                         "frac": tf4 / pk["tflops"], "frac_of_nominal_2250": tf4 / 2250.0,
+                         "traffic": TRAFFIC["cfg4"]},
             "config": {"workload": "cfg4: block-sparse causal prefill bf16 B=2 H=16 S=16384 D=128, 64x64 "
                                    "blocks, 8-block window + Bernoulli(0.1) earlier blocks seed 3",
                        "flops": "4*D per visible (query,key) pair of the listed blocks only"}}
@@ -269,7 +274,7 @@ def run_ours(args, rank, world, local_rank):
             "value": gbs5 * world, "unit": "GB/s", "ms_per_step": ms5,
             "roofline": {"bound": "hbm", "achieved": gbs5, "peak": pk["gbs"], "unit": "GB/s",
                          "frac": gbs5 / pk["gbs"], "frac_of_nominal_8TBs": gbs5 / 8000.0,
-                         "traffic": None},
+                         "traffic": TRAFFIC["cfg5"], "algorithmic_bytes": w5.kv_bytes},
             "config": {"workload": "cfg5: block-sparse decode bf16 B=32 H=32 D=128, KV 32768 = 512 "
                                    "blocks of 64, 64 blocks per (b,h) seed 4"}}
         del w5
@@ -295,7 +300,8 @@ def run_ours(args, rank, world, local_rank):
                      "peak_source": pk["source"] + " cuBLAS bf16 burst",
                      "frac_of_sustained": per_launch_tflops / pk["tflops_sustained"] if pk["tflops_sustained"] else None,
                      "frac_of_nominal_2250": per_launch_tflops / 2250.0,
-                     "traffic": None},
+                     "traffic": TRAFFIC["cfg2"], "traffic_unit": "bytes per launch (ncu)",
+                     "algorithmic_bytes": 4 * w.q.numel() * 2 + w.q.numel() // 128 * 4},
         "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": total_flops / ms_e2e / 1e9, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
