@@ -104,3 +104,38 @@ def test_ops_reject_cpu_tensors(lib):
     kv = torch.zeros(1, 8, 2, 64, dtype=torch.float16)
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         ops.decode(q, kv, kv, seqlens=torch.tensor([8], dtype=torch.int32))
+
+
+def test_prefill_validation_codes(lib):
+    from tritonops_b200._lib import PrefillArgs
+    a = PrefillArgs()
+    assert lib.b200attn_prefill_fwd(C.byref(a), None) == -1            # NULL pointers
+    a.q = a.k = a.v = a.o = 0x1000
+    a.dtype = 3
+    assert lib.b200attn_prefill_fwd(C.byref(a), None) == -2
+    a.dtype, a.head_dim = 1, 80
+    assert lib.b200attn_prefill_fwd(C.byref(a), None) == -3
+    a.head_dim, a.batch, a.heads_q, a.heads_kv = 128, 1, 5, 2
+    assert lib.b200attn_prefill_fwd(C.byref(a), None) == -4
+    a.heads_q = 4
+    assert lib.b200attn_prefill_fwd(C.byref(a), None) == -7            # seqlen 0, no cu_seqlens
+    a.seqlen = 256
+    a.k = 0x1004
+    assert lib.b200attn_prefill_fwd(C.byref(a), None) == -5
+    a.k, a.v_stride_t = 0x1000, 12
+    assert lib.b200attn_prefill_fwd(C.byref(a), None) == -6
+    a.v_stride_t, a.softmax_scale = 256, 0.0
+    assert lib.b200attn_prefill_fwd(C.byref(a), None) == -7            # scale must be positive
+    a.softmax_scale = 0.1
+    a.sparsity = 2                                                      # block list without lists
+    assert lib.b200attn_sparse_prefill_fwd(C.byref(a), None) == -1
+    a.block_idx = a.block_cnt = 0x1000
+    a.block_size, a.n_qblocks, a.max_nnz = 32, 4, 4
+    assert lib.b200attn_sparse_prefill_fwd(C.byref(a), None) == -9     # only 64-token blocks
+    a.block_size, a.seqlen = 64, 64 * 2048 + 1
+    assert lib.b200attn_sparse_prefill_fwd(C.byref(a), None) == -11    # list capacity exceeded
+    a.sparsity, a.window_local = 1, -1
+    assert lib.b200attn_sparse_prefill_fwd(C.byref(a), None) == -9
+    a.sparsity = 9
+    assert lib.b200attn_sparse_prefill_fwd(C.byref(a), None) == -9
+    assert lib.b200attn_prefill_workspace_bytes(C.byref(a)) == 0

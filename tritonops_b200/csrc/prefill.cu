@@ -176,16 +176,17 @@ struct PrefillSmem {
   static constexpr int kKvPanel = BN * 128;
   static constexpr int kBarOffset = 2 * kQBytes + NSTAGE * kStageBytes;
   static constexpr int kNumBars = 2 + 2 * NSTAGE + 6;
-  // block-list mode: 4 bitmaps (one per 64-row query block of the CTA), then the
-  // merged ascending list of KV blocks with a 4-bit membership mask each
+  // block-list mode: 4 bitmaps (one per 64-row query block of the CTA), then per
+  // query tile the merged ascending list of KV blocks with a 2-bit membership mask
   static constexpr int kBitmapOffset = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kUlistOffset = kBitmapOffset + 4 * (kMaxBlocks / 32) * 4;
-  static constexpr int kUflagOffset = kUlistOffset + kMaxBlocks * 2;
-  static constexpr int kBytes = kUflagOffset + kMaxBlocks;
+  static constexpr int kUflagOffset = kUlistOffset + 2 * kMaxBlocks * 2;
+  static constexpr int kBytes = kUflagOffset + 2 * kMaxBlocks;
   static constexpr int kAlloc = kBytes + 1024;  // slack to align the base to 1024 bytes
 };
 
-template <typename T, int DP, int BN, int NSTAGE>
+// BLK: block-list sparsity (own instantiation so the dense / window paths carry none of its branches)
+template <typename T, int DP, int BN, int NSTAGE, bool BLK>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
@@ -258,16 +259,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   auto tS = [&](int t) { return tmem + 128u * t; };
   auto tO = [&](int t) { return tmem + 256u + 128u * t; };
 
-  // ---- block-list mode: merge the lists of the CTA's four query blocks into one
-  // ascending list of KV blocks (two blocks form one 128-key step) with a
-  // membership mask per entry.  Entries out of range, or above the diagonal
-  // when causal, are dropped here, so nothing later can index out of bounds.
-  const bool blk = p.block_idx != nullptr;
+  // ---- block-list mode: each 128-row query tile walks the union of the lists
+  // of its two 64-row query blocks, two KV blocks per 128-key step, with its own
+  // K/V stream.  The union is built as a bitmap per query block, merged and
+  // compacted into an ascending list with a 2-bit membership mask per entry.
+  // Entries out of range, or above the diagonal when causal, are dropped here,
+  // so nothing later can index out of bounds.
+  constexpr bool blk = BLK;
   unsigned int* bitmap = reinterpret_cast<unsigned int*>(smem_gen + L::kBitmapOffset);
-  volatile unsigned short* ulist = reinterpret_cast<volatile unsigned short*>(smem_gen + L::kUlistOffset);
-  volatile unsigned char* uflags = reinterpret_cast<volatile unsigned char*>(smem_gen + L::kUflagOffset);
+  volatile unsigned short* ulist_all = reinterpret_cast<volatile unsigned short*>(smem_gen + L::kUlistOffset);
+  volatile unsigned char* uflags_all = reinterpret_cast<volatile unsigned char*>(smem_gen + L::kUflagOffset);
   volatile int* n_u_slot = reinterpret_cast<volatile int*>(smem_gen + L::kBarOffset + L::kNumBars * 8 + 8);
-  int n_u = 0;
+  auto ulist = [&](int t, int i) -> int { return (int)ulist_all[t * kMaxBlocks + i]; };
+  auto uflags = [&](int t, int i) -> unsigned { return (unsigned)uflags_all[t * kMaxBlocks + i]; };
+  int n_u[2] = {0, 0};
   if (blk) {
     constexpr int kWords = kMaxBlocks / 32;
     for (int i = threadIdx.x; i < 4 * kWords; i += kPrefillThreads) bitmap[i] = 0u;
@@ -286,13 +291,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
     }
     __syncthreads();
-    if (warp == 0) {
+    if (warp < 2) {
+      const int t = warp;
       int base = 0;
       for (int w0 = 0; w0 < kWords; w0 += 32) {
         const int w = w0 + lane;
-        const unsigned m0 = bitmap[w], m1 = bitmap[kWords + w], m2 = bitmap[2 * kWords + w],
-                       m3 = bitmap[3 * kWords + w];
-        unsigned any = m0 | m1 | m2 | m3;
+        const unsigned m0 = bitmap[(2 * t) * kWords + w], m1 = bitmap[(2 * t + 1) * kWords + w];
+        unsigned any = m0 | m1;
         const int cnt = __popc(any);
         int incl = cnt;
 #pragma unroll
@@ -304,25 +309,26 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         while (any) {
           const int bit = __ffs(any) - 1;
           any &= any - 1;
-          ulist[pos] = (unsigned short)(w * 32 + bit);
-          uflags[pos] = (unsigned char)(((m0 >> bit) & 1u) | (((m1 >> bit) & 1u) << 1) |
-                                        (((m2 >> bit) & 1u) << 2) | (((m3 >> bit) & 1u) << 3));
+          ulist_all[t * kMaxBlocks + pos] = (unsigned short)(w * 32 + bit);
+          uflags_all[t * kMaxBlocks + pos] = (unsigned char)(((m0 >> bit) & 1u) | (((m1 >> bit) & 1u) << 1));
           ++pos;
         }
         base += __shfl_sync(0xffffffffu, incl, 31);
       }
-      if (lane == 0) *n_u_slot = base;
+      if (lane == 0) n_u_slot[t] = base;
     }
     __syncthreads();
-    n_u = *n_u_slot;
+    n_u[0] = n_u_slot[0];
+    n_u[1] = n_u_slot[1];
   }
-  const int n_steps = blk ? (n_u + 1) / 2 : seq.n;
+  // steps of each tile in block-list mode (its own K/V stream), else of the CTA
+  const int ns0 = (q0 < len) ? (n_u[0] + 1) / 2 : 0;
+  const int ns1 = (q0 + kTileM < len) ? (n_u[1] + 1) / 2 : 0;
+  const int n_steps = blk ? max(ns0, ns1) : seq.n;
   // does query tile t take part in step j?
   auto step_active = [&](int t, int j) -> bool {
     if (!blk) return tile_active<BN>(p, q0 + kTileM * t, len, seq.kv(j));
-    unsigned f = uflags[2 * j];
-    if (2 * j + 1 < n_u) f |= uflags[2 * j + 1];
-    return (q0 + kTileM * t < len) && ((f >> (2 * t)) & 3u) != 0u;
+    return j < (t ? ns1 : ns0);
   };
 
   if (warp >= 8) {
@@ -343,31 +349,45 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         __syncwarp();
       }
       int cnt = 0;
-      for (int j = 0; j < n_steps; ++j) {
-        // dense / window: one 128-row box; block list: two 64-row boxes (the K/V
-        // tensor maps are then built with 64-row boxes), the second repeating the
-        // first when the list has an odd length (its columns are masked)
-        int row0, row1 = 0;
-        if (blk) {
-          row0 = seq_start + (int)ulist[2 * j] * kBlk;
-          row1 = seq_start + (int)ulist[min(2 * j + 1, n_u - 1)] * kBlk;
-        } else {
-          row0 = seq_start + seq.kv(j) * BN;
-        }
-        for (int which = 0; which < 2; ++which, ++cnt) {
-          const int s = cnt % NSTAGE;
-          const uint32_t ph = (cnt / NSTAGE) & 1;
-          mbar_wait(kv_empty(s), ph ^ 1, abort_flag);
-          if (elect_one()) {
-            mbar_expect_tx(kv_full(s), L::kStageBytes);
-            const CUtensorMap* m = which ? &tmap_v : &tmap_k;
-            for (int pn = 0; pn < kPanels; ++pn) {
-              const uint32_t dst = sKV + s * L::kStageBytes + pn * L::kKvPanel;
-              tma_load_4d(dst, m, kv_full(s), 64 * pn, row0, hk, bcoord);
-              if (blk) tma_load_4d(dst + kBlk * 128, m, kv_full(s), 64 * pn, row1, hk, bcoord);
-            }
+      // one stage: a 128-row box (dense / window) or two 64-row boxes (block list;
+      // the K/V tensor maps are then built with 64-row boxes)
+      auto load_stage = [&](const CUtensorMap* m, int row0, int row1, bool two) {
+        const int s = cnt % NSTAGE;
+        const uint32_t ph = (cnt / NSTAGE) & 1;
+        mbar_wait(kv_empty(s), ph ^ 1, abort_flag);
+        if (elect_one()) {
+          mbar_expect_tx(kv_full(s), L::kStageBytes);
+          for (int pn = 0; pn < kPanels; ++pn) {
+            const uint32_t dst = sKV + s * L::kStageBytes + pn * L::kKvPanel;
+            tma_load_4d(dst, m, kv_full(s), 64 * pn, row0, hk, bcoord);
+            if (two) tma_load_4d(dst + kBlk * 128, m, kv_full(s), 64 * pn, row1, hk, bcoord);
           }
-          __syncwarp();
+        }
+        __syncwarp();
+        ++cnt;
+      };
+      if (!blk) {
+        for (int j = 0; j < n_steps; ++j) {
+          const int row = seq_start + seq.kv(j) * BN;
+          load_stage(&tmap_k, row, 0, false);
+          load_stage(&tmap_v, row, 0, false);
+        }
+      } else {
+        // per tile its own stream, in the order the MMA warp consumes the stages:
+        // K(0,0) K(1,0), then per step V(0,j) K(0,j+1) V(1,j) K(1,j+1).  An odd
+        // list repeats its last block in the second box (those columns are masked).
+        auto load_blk = [&](const CUtensorMap* m, int t, int j) {
+          const int nu = n_u[t];
+          load_stage(m, seq_start + ulist(t, 2 * j) * kBlk,
+                     seq_start + ulist(t, min(2 * j + 1, nu - 1)) * kBlk, true);
+        };
+        if (ns0 > 0) load_blk(&tmap_k, 0, 0);
+        if (ns1 > 0) load_blk(&tmap_k, 1, 0);
+        for (int j = 0; j < n_steps; ++j) {
+          if (j < ns0) load_blk(&tmap_v, 0, j);
+          if (j + 1 < ns0) load_blk(&tmap_k, 0, j + 1);
+          if (j < ns1) load_blk(&tmap_v, 1, j);
+          if (j + 1 < ns1) load_blk(&tmap_k, 1, j + 1);
         }
       }
       // every issued copy must have landed before the CTA may exit
@@ -420,22 +440,35 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (issue) TRACE(20 + t);
         ++pv_cnt[t];
       };
-      int sK = n_steps > 0 ? wait_stage() : 0;
-      for (int t = 0; t < 2; ++t)
-        if (n_steps > 0 && step_active(t, 0)) issue_qk(t, sK);
-      if (n_steps > 0) mma_commit(kv_empty(sK), issue);
-      for (int j = 0; j < n_steps; ++j) {
-        const int sV = wait_stage();
-        const bool more = j + 1 < n_steps;
-        int sKn = 0;
-        for (int t = 0; t < 2; ++t) {
-          const int q0t = q0 + kTileM * t;
-          if (step_active(t, j)) issue_pv(t, sV);
-          if (t == 1) mma_commit(kv_empty(sV), issue);
-          if (more) {
-            if (t == 0) sKn = wait_stage();
-            if (step_active(t, j + 1)) issue_qk(t, sKn);
-            if (t == 1) mma_commit(kv_empty(sKn), issue);
+      if (!blk) {
+        // both tiles share every K/V stage
+        int sK = n_steps > 0 ? wait_stage() : 0;
+        for (int t = 0; t < 2; ++t)
+          if (n_steps > 0 && step_active(t, 0)) issue_qk(t, sK);
+        if (n_steps > 0) mma_commit(kv_empty(sK), issue);
+        for (int j = 0; j < n_steps; ++j) {
+          const int sV = wait_stage();
+          const bool more = j + 1 < n_steps;
+          int sKn = 0;
+          for (int t = 0; t < 2; ++t) {
+            if (step_active(t, j)) issue_pv(t, sV);
+            if (t == 1) mma_commit(kv_empty(sV), issue);
+            if (more) {
+              if (t == 0) sKn = wait_stage();
+              if (step_active(t, j + 1)) issue_qk(t, sKn);
+              if (t == 1) mma_commit(kv_empty(sKn), issue);
+            }
+          }
+        }
+      } else {
+        // block lists: each tile consumes its own stages (same order as the loader)
+        for (int t = 0; t < 2; ++t)
+          if ((t ? ns1 : ns0) > 0) { const int s = wait_stage(); issue_qk(t, s); mma_commit(kv_empty(s), issue); }
+        for (int j = 0; j < n_steps; ++j) {
+          for (int t = 0; t < 2; ++t) {
+            const int ns = t ? ns1 : ns0;
+            if (j < ns) { const int s = wait_stage(); issue_pv(t, s); mma_commit(kv_empty(s), issue); }
+            if (j + 1 < ns) { const int s = wait_stage(); issue_qk(t, s); mma_commit(kv_empty(s), issue); }
           }
         }
       }
@@ -465,22 +498,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int cc = 0; cc < BN / 32; ++cc) tmem_ld32(tS(t) + lane_off + 32 * cc, &sr[32 * cc]);
         tmem_wait_ld();
         if (row == 0) TRACE(40 + t);
+        bool vis0 = true, vis1 = true;   // does this warp's query block see each 64-column half?
         if (blk) {
           // columns [0,64) belong to KV block u0, [64,128) to u1; a row sees a
           // prefix of each half: nothing if its query block does not list the KV
           // block, else up to the causal diagonal and the sequence end
-          const int u0 = ulist[2 * j];
-          const bool has1 = 2 * j + 1 < n_u;
-          const int u1 = has1 ? (int)ulist[2 * j + 1] : 0;
-          const unsigned f0 = uflags[2 * j], f1 = has1 ? (unsigned)uflags[2 * j + 1] : 0u;
-          const unsigned tile_bits = 3u << (2 * t);
-          bool full = has1 && (f0 & tile_bits) == tile_bits && (f1 & tile_bits) == tile_bits &&
-                      (u1 + 1) * kBlk <= len && (u0 + 1) * kBlk <= len;
+          const int u0 = ulist(t, 2 * j);
+          const bool has1 = 2 * j + 1 < n_u[t];
+          const int u1 = has1 ? ulist(t, 2 * j + 1) : 0;
+          const unsigned f0 = uflags(t, 2 * j), f1 = has1 ? uflags(t, 2 * j + 1) : 0u;
+          bool full = has1 && f0 == 3u && f1 == 3u && (u1 + 1) * kBlk <= len && (u0 + 1) * kBlk <= len;
           if (p.causal) full = full && (u1 + 1) * kBlk - 1 <= q0t && (u0 + 1) * kBlk - 1 <= q0t;
+          const int qa = row >> 6;                 // query block inside the tile (uniform per warp)
+          vis0 = (f0 >> qa) & 1u;
+          vis1 = (f1 >> qa) & 1u;
           if (!full) {
-            const int qbl = 2 * t + (row >> 6);
-            int lim0 = ((f0 >> qbl) & 1u) ? min(kBlk, len - u0 * kBlk) : 0;
-            int lim1 = ((f1 >> qbl) & 1u) ? min(kBlk, len - u1 * kBlk) : 0;
+            int lim0 = vis0 ? min(kBlk, len - u0 * kBlk) : 0;
+            int lim1 = vis1 ? min(kBlk, len - u1 * kBlk) : 0;
             if (p.causal) { lim0 = min(lim0, qi - u0 * kBlk + 1); lim1 = min(lim1, qi - u1 * kBlk + 1); }
 #pragma unroll
             for (int x = 0; x < kBlk; ++x) {
@@ -511,11 +545,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int x = 0; x < BN; x += 8) {
-          mx0 = fmax3(mx0, __uint_as_float(sr[x]), __uint_as_float(sr[x + 1]));
-          mx1 = fmax3(mx1, __uint_as_float(sr[x + 2]), __uint_as_float(sr[x + 3]));
-          mx2 = fmax3(mx2, __uint_as_float(sr[x + 4]), __uint_as_float(sr[x + 5]));
-          mx3 = fmax3(mx3, __uint_as_float(sr[x + 6]), __uint_as_float(sr[x + 7]));
+        for (int hb = 0; hb < 2; ++hb) {
+          if (hb == 0 ? vis0 : vis1) {   // (warp-uniform) an unlisted half is all -inf
+#pragma unroll
+            for (int x = hb * (BN / 2); x < (hb + 1) * (BN / 2); x += 8) {
+              mx0 = fmax3(mx0, __uint_as_float(sr[x]), __uint_as_float(sr[x + 1]));
+              mx1 = fmax3(mx1, __uint_as_float(sr[x + 2]), __uint_as_float(sr[x + 3]));
+              mx2 = fmax3(mx2, __uint_as_float(sr[x + 4]), __uint_as_float(sr[x + 5]));
+              mx3 = fmax3(mx3, __uint_as_float(sr[x + 6]), __uint_as_float(sr[x + 7]));
+            }
+          }
         }
         const float m_new = fmax3(m_run, fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         // keep the stale max unless it is too far behind (first tile: always take)
@@ -543,15 +582,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         uint32_t pr[BN / 2];
         const float neg_mc = -mc;
 #pragma unroll
-        for (int x = 0; x < BN / 2; x += 2) {
-          float e0, e1, e2, e3;
-          ffma2(e0, e1, __uint_as_float(sr[2 * x]), __uint_as_float(sr[2 * x + 1]), c, neg_mc);
-          ffma2(e2, e3, __uint_as_float(sr[2 * x + 2]), __uint_as_float(sr[2 * x + 3]), c, neg_mc);
-          e0 = ex2(e0); e1 = ex2(e1); e2 = ex2(e2); e3 = ex2(e3);
-          fadd2(sum0, sum1, e0, e1);
-          fadd2(sum2, sum3, e2, e3);
-          pr[x] = pack2<T>(e0, e1);
-          pr[x + 1] = pack2<T>(e2, e3);
+        for (int hb = 0; hb < 2; ++hb) {
+          if (hb == 0 ? vis0 : vis1) {
+#pragma unroll
+            for (int x = hb * (BN / 4); x < (hb + 1) * (BN / 4); x += 2) {
+              float e0, e1, e2, e3;
+              ffma2(e0, e1, __uint_as_float(sr[2 * x]), __uint_as_float(sr[2 * x + 1]), c, neg_mc);
+              ffma2(e2, e3, __uint_as_float(sr[2 * x + 2]), __uint_as_float(sr[2 * x + 3]), c, neg_mc);
+              e0 = ex2(e0); e1 = ex2(e1); e2 = ex2(e2); e3 = ex2(e3);
+              fadd2(sum0, sum1, e0, e1);
+              fadd2(sum2, sum3, e2, e3);
+              pr[x] = pack2<T>(e0, e1);
+              pr[x + 1] = pack2<T>(e2, e3);
+            }
+          } else {   // block-list mode: this query block does not list that KV block
+#pragma unroll
+            for (int x = hb * (BN / 4); x < (hb + 1) * (BN / 4); ++x) pr[x] = 0u;
+          }
         }
         sum0 += sum2; sum1 += sum3;
         if (row == 0) TRACE(60 + t);
@@ -699,15 +746,15 @@ static int launch_prefill(const b200attn_prefill_args* a, const PrefillParams& p
       !make_tmap(&tk, a->dtype, a->k, a->head_dim, tokens, a->heads_kv, tb, a->k_stride_t, a->k_stride_h, a->k_stride_b, p.block_idx ? kBlk : BN) ||
       !make_tmap(&tv, a->dtype, a->v, a->head_dim, tokens, a->heads_kv, tb, a->v_stride_t, a->v_stride_h, a->v_stride_b, p.block_idx ? kBlk : BN))
     return B200ATTN_ERR_CUDA;
-  auto kern = prefill_kernel<T, DP, BN, NSTAGE>;
-  static bool attr_set = false;  // per instantiation; setting it twice is harmless
-  if (!attr_set) {
+  auto kern = p.block_idx ? prefill_kernel<T, DP, BN, NSTAGE, true> : prefill_kernel<T, DP, BN, NSTAGE, false>;
+  static bool attr_set[2] = {false, false};  // per instantiation and mode; setting it twice is harmless
+  if (!attr_set[p.block_idx ? 1 : 0]) {
     cudaFuncAttributes fa;
     if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return B200ATTN_ERR_CUDA;
     if (fa.numRegs < kLaunchRegs) return B200ATTN_ERR_CUDA;  // register hand-over would not balance
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
       return B200ATTN_ERR_CUDA;
-    attr_set = true;
+    attr_set[p.block_idx ? 1 : 0] = true;
   }
   const long long blocks = (long long)p.n_pairs * a->heads_q * a->batch;
   if (blocks <= 0) return B200ATTN_OK;
