@@ -180,6 +180,52 @@ int b200attn_sparse_decode_fwd(const b200attn_decode_args* args, b200attn_stream
 #define B200ATTN_NOALLOC_SCRATCH_BYTES (32u << 20)
 int b200attn_decode_fwd_noalloc(const b200attn_decode_args* args, b200attn_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Dense prefill backward.  Tensors and addressing forms as in
+ * b200attn_prefill_args; o and lse are the forward's outputs, d_o the
+ * gradient of o; dq like q, dk / dv like k / v (the query heads of a GQA group
+ * are summed into their KV head).  Workspace: fp32 dq accumulator + row sums.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_o;
+  const float* lse;
+  void* dq;
+  void* dk;
+  void* dv;
+  int32_t dtype;
+  int32_t batch, heads_q, heads_kv, head_dim;
+  int32_t seqlen, max_seqlen;
+  int64_t total_tokens;
+  const int32_t* cu_seqlens;
+  int64_t q_stride_b, q_stride_t, q_stride_h;
+  int64_t k_stride_b, k_stride_t, k_stride_h;
+  int64_t v_stride_b, v_stride_t, v_stride_h;
+  int64_t o_stride_b, o_stride_t, o_stride_h;
+  int64_t do_stride_b, do_stride_t, do_stride_h;
+  int64_t dq_stride_b, dq_stride_t, dq_stride_h;
+  int64_t dk_stride_b, dk_stride_t, dk_stride_h;
+  int64_t dv_stride_b, dv_stride_t, dv_stride_h;
+  int64_t lse_stride_b, lse_stride_t, lse_stride_h;
+  float softmax_scale;
+  int32_t scale_has_log2e;
+  int32_t causal;
+  int32_t lse_base2;           /* form of `lse`, as written by the forward */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status_word;
+} b200attn_prefill_bwd_args;
+
+size_t b200attn_prefill_bwd_workspace_bytes(const b200attn_prefill_bwd_args* args);
+
+/* dQ, dK, dV of the dense causal / non-causal forward.  Replaces
+ * flash_attn_triton_bwd (flash_attn_triton/flash_attn_triton.py:661-813) and
+ * its kernels (:184-592). */
+int b200attn_prefill_bwd(const b200attn_prefill_bwd_args* args, b200attn_stream_t stream);
+
 /* Prefill needs no scratch; kept so callers can size buffers uniformly. */
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args* args);
 

@@ -95,6 +95,38 @@ def dense_prefill_exact(q, k, v, cu_seq_lens, *, causal=True, scale=None,
     return o, lse
 
 
+def dense_prefill_grads_exact(q, k, v, cu_seq_lens, d_o, *, causal=True, scale=None,
+                              dtype=torch.float32):
+    """dQ, dK, dV of dense_prefill_exact by autograd in ``dtype`` (the math of
+    flash_attn_triton_bwd, flash_attn_triton/flash_attn_triton.py:184-592: D =
+    rowsum(dO o O), dS = P o (dP - D), dQ = scale dS K, dK = scale dS^T Q, dV =
+    P^T dO, with dK / dV summed over each GQA group, :813)."""
+    qf = q.detach().to(dtype).requires_grad_(True)
+    kf = k.detach().to(dtype).requires_grad_(True)
+    vf = v.detach().to(dtype).requires_grad_(True)
+    _, T, Hq, D = q.shape
+    Hkv = k.shape[2]
+    g = Hq // Hkv
+    if scale is None:
+        scale = D ** -0.5
+    loss = qf.sum() * 0
+    for s0, s1 in _lens(cu_seq_lens):
+        n = s1 - s0
+        if n <= 0:
+            continue
+        bq = qf[0, s0:s1].permute(1, 0, 2)
+        bk = kf[0, s0:s1].permute(1, 0, 2).repeat_interleave(g, 0)
+        bv = vf[0, s0:s1].permute(1, 0, 2).repeat_interleave(g, 0)
+        s = torch.matmul(bq, bk.transpose(1, 2)) * scale
+        if causal:
+            idx = torch.arange(n)
+            s = s.masked_fill(~(idx[:, None] >= idx[None, :]), -math.inf)
+        o = torch.matmul(torch.softmax(s, -1), bv).permute(1, 0, 2)        # [n, Hq, Dv]
+        loss = loss + (o * d_o[0, s0:s1].to(dtype)).sum()
+    loss.backward()
+    return qf.grad, kf.grad, vf.grad
+
+
 def dense_prefill_refpath(q, k, v, cu_seq_lens):
     """Restatement of flash_attn_torch (flash_attn_triton/flash_attn_triton.py:877-915):
     scores in the input dtype, causal fill, fp32 softmax, P cast back to the

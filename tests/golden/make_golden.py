@@ -71,6 +71,13 @@ def gen_torch():
     for name in ("dense_a", "dense_b", "dense_c"):
         i = build(name)
         put(name, o=dense.flash_attn_torch(i["q"], i["k"], i["v"], i["cu"]), insum=checksum(i))
+        # gradients of the reference's torch path by autograd, as its own test does
+        # (flash_attn_triton.py:1053-1063), with a seeded dO
+        q, k, v = (i[n].clone().requires_grad_(True) for n in "qkv")
+        o = dense.flash_attn_torch(q, k, v, i["cu"])
+        do = torch.randn(o.shape, generator=torch.Generator().manual_seed(1234)).to(o.dtype)
+        (o * do).sum().backward()
+        put(name, do=do, dq=q.grad, dk=k.grad, dv=v.grad)
 
     # config 1: causal via flash_attn_torch; non-causal via the tutorial's
     # torch_full_attention, whose module runs CUDA code at import, so only

@@ -41,13 +41,15 @@ def test_struct_sizes_match_header(lib):
         src = os.path.join(d, "p.c")
         open(src, "w").write(
             '#include <stdio.h>\n#include <stddef.h>\n#include "b200attn.h"\n'
-            'int main(){printf("%zu %zu %zu %zu\\n", sizeof(b200attn_prefill_args),'
+            'int main(){printf("%zu %zu %zu %zu %zu %zu\\n", sizeof(b200attn_prefill_args),'
             ' sizeof(b200attn_decode_args), offsetof(b200attn_prefill_args, status_word),'
-            ' offsetof(b200attn_decode_args, workspace_bytes));return 0;}\n')
+            ' offsetof(b200attn_decode_args, workspace_bytes), sizeof(b200attn_prefill_bwd_args),'
+            ' offsetof(b200attn_prefill_bwd_args, workspace_bytes));return 0;}\n')
         exe = os.path.join(d, "p")
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), src, "-o", exe])
-        a, b, c, e = map(int, subprocess.check_output([exe]).split())
+        a, b, c, e, f, g = map(int, subprocess.check_output([exe]).split())
     assert a == C.sizeof(_lib.PrefillArgs) and b == C.sizeof(_lib.DecodeArgs)
+    assert f == C.sizeof(_lib.PrefillBwdArgs) and g == _lib.PrefillBwdArgs.workspace_bytes.offset
     assert c == _lib.PrefillArgs.status_word.offset
     assert e == _lib.DecodeArgs.workspace_bytes.offset
 
@@ -139,3 +141,22 @@ def test_prefill_validation_codes(lib):
     a.sparsity = 9
     assert lib.b200attn_sparse_prefill_fwd(C.byref(a), None) == -9
     assert lib.b200attn_prefill_workspace_bytes(C.byref(a)) == 0
+
+
+def test_prefill_bwd_validation_codes(lib):
+    from tritonops_b200._lib import PrefillBwdArgs
+    a = PrefillBwdArgs()
+    assert lib.b200attn_prefill_bwd(C.byref(a), None) == -1
+    for n in ("q", "k", "v", "o", "d_o", "lse", "dq", "dk", "dv"):
+        setattr(a, n, 0x1000)
+    a.dtype, a.head_dim, a.batch, a.heads_q, a.heads_kv, a.seqlen = 1, 128, 2, 8, 2, 256
+    a.softmax_scale = 0.1
+    assert lib.b200attn_prefill_bwd(C.byref(a), None) == -8          # no workspace
+    rows = 2 * 256 * 8
+    assert lib.b200attn_prefill_bwd_workspace_bytes(C.byref(a)) == rows * 128 * 4 + rows * 4
+    a.head_dim = 96
+    assert lib.b200attn_prefill_bwd_workspace_bytes(C.byref(a)) == rows * 128 * 4 + rows * 4
+    a.head_dim = 64
+    assert lib.b200attn_prefill_bwd_workspace_bytes(C.byref(a)) == rows * 64 * 4 + rows * 4
+    a.dk_stride_t = 4
+    assert lib.b200attn_prefill_bwd(C.byref(a), None) == -6

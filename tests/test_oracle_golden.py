@@ -162,3 +162,16 @@ def test_block_sparse_decoding_full_list_equals_dense():
     a = orc.decoding_exact(i["q"], i["kc"], i["vc"], lens)
     b = orc.block_sparse_decoding_exact(i["q"], i["kc"], i["vc"], lens, idx)
     assert maxabs(a, b) <= 1e-5
+
+
+@pytest.mark.parametrize("name", ["dense_a", "dense_b", "dense_c"])
+def test_grads_exact_vs_reference_autograd(name):
+    """fp32 gradients of the oracle against the reference torch path's autograd
+    gradients (bf16 arithmetic): the reference test's tolerances
+    (flash_attn_triton.py:1086-1089)."""
+    i = build(name)
+    g = GT[name]
+    dq, dk, dv = orc.dense_prefill_grads_exact(i["q"], i["k"], i["v"], i["cu"], g["do"])
+    torch.testing.assert_close(dq, g["dq"].float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(dk, g["dk"].float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(dv, g["dv"].float(), rtol=1e-1, atol=1e-1)

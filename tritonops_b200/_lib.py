@@ -47,6 +47,19 @@ class DecodeArgs(C.Structure):
     ]
 
 
+class PrefillBwdArgs(C.Structure):
+    _fields_ = [
+        ("q", vp), ("k", vp), ("v", vp), ("o", vp), ("d_o", vp), ("lse", vp),
+        ("dq", vp), ("dk", vp), ("dv", vp),
+        ("dtype", i32), ("batch", i32), ("heads_q", i32), ("heads_kv", i32), ("head_dim", i32),
+        ("seqlen", i32), ("max_seqlen", i32), ("total_tokens", i64), ("cu_seqlens", vp),
+    ] + [(f"{n}_stride_{a}", i64) for n in ("q", "k", "v", "o", "do", "dq", "dk", "dv", "lse")
+         for a in ("b", "t", "h")] + [
+        ("softmax_scale", f32), ("scale_has_log2e", i32), ("causal", i32), ("lse_base2", i32),
+        ("workspace", vp), ("workspace_bytes", C.c_size_t), ("status_word", vp),
+    ]
+
+
 # every symbol include/b200attn.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "b200attn_abi_version": (C.c_int, []),
@@ -59,6 +72,8 @@ SYMBOLS = {
     "b200attn_decode_fwd": (C.c_int, [C.POINTER(DecodeArgs), vp]),
     "b200attn_sparse_decode_fwd": (C.c_int, [C.POINTER(DecodeArgs), vp]),
     "b200attn_decode_fwd_noalloc": (C.c_int, [C.POINTER(DecodeArgs), vp]),
+    "b200attn_prefill_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(PrefillBwdArgs)]),
+    "b200attn_prefill_bwd": (C.c_int, [C.POINTER(PrefillBwdArgs), vp]),
 }
 NOALLOC_SCRATCH_BYTES = 32 << 20
 

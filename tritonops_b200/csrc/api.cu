@@ -53,6 +53,15 @@ int b200attn_decode_fwd_noalloc(const b200attn_decode_args* args, b200attn_strea
   return decode_fwd_noalloc(args, (cudaStream_t)stream);
 }
 
+size_t b200attn_prefill_bwd_workspace_bytes(const b200attn_prefill_bwd_args* args) {
+  return prefill_bwd_workspace_bytes(args);
+}
+
+int b200attn_prefill_bwd(const b200attn_prefill_bwd_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return prefill_bwd(args, (cudaStream_t)stream);
+}
+
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args*) { return 0; }
 
 int b200attn_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream) {

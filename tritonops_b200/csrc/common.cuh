@@ -18,6 +18,8 @@ int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t
                cudaStream_t stream);
 int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream);
 int decode_fwd_noalloc(const b200attn_decode_args* a, cudaStream_t stream);
+size_t prefill_bwd_workspace_bytes(const b200attn_prefill_bwd_args* a);
+int prefill_bwd(const b200attn_prefill_bwd_args* a, cudaStream_t stream);
 
 // 16-byte read-only load that does not pollute L1 (data is used once).
 template <typename T>

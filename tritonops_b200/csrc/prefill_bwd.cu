@@ -1,0 +1,517 @@
+// Dense prefill backward for sm_100a (dQ, dK, dV of causal / non-causal varlen GQA
+// attention).  Stands in for flash_attn_triton_bwd and its three kernels
+// (flash_attn_triton/flash_attn_triton.py:184-592, :661-813).
+//
+//   D_i  = sum_d dO_i O_i                                   (bwd_rowsum_kernel)
+//   P    = exp2(Q K^T c - lse2)        dP = dO V^T
+//   dS   = P o (dP - D)
+//   dV  += P^T dO     dK += scale dS^T Q     dQ += scale dS K
+//
+// One CTA owns one 128-key tile of one (sequence, KV head) and walks every
+// query head of the GQA group and every 128-row query tile that can see it:
+// dK and dV of the tile accumulate in tensor memory across that whole walk
+// (which also sums the group's query heads, done on the host in the
+// reference, :813), dQ tiles are added to an fp32 accumulator in global memory
+// with vector reductions and converted at the end.  All five products are
+// tcgen05.mma: S and dP with both operands K-major from shared memory; P and
+// dS are written by the softmax threads into 128-byte-swizzled shared memory
+// once and read twice, as the MN-major A operand of dV / dK and as the K-major
+// A operand of dQ.  TMEM columns: S then dQ [0,128), dP [128,256), dK
+// [256,384), dV [384,512).  This first version runs the steps of one (query
+// tile, key tile) pair one after the other (no software pipelining).
+#include <type_traits>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace b200attn {
+using namespace sm100;
+
+namespace {
+
+constexpr int kBwdThreads = 160;   // warps 0-3: one thread per row; warp 4: TMA + MMA issue
+constexpr int kT = 128;            // rows / keys per tile
+
+struct BwdParams {
+  const float* lse;
+  const float* dvec;       // D, fp32 [tokens, heads_q]
+  float* dq_acc;           // fp32 [tokens, heads_q, DP]
+  void* dk;
+  void* dv;
+  const int32_t* cu_seqlens;
+  long long lse_sb, lse_st, lse_sh;
+  long long dk_sb, dk_st, dk_sh, dv_sb, dv_st, dv_sh;
+  int batch, heads_q, heads_kv, group, head_dim;
+  int seqlen, n_kvtiles;
+  int causal;
+  float scale_log2, scale;   // q.k multiplier in base-2 and natural form
+  int lse_base2;
+  int* status_word;
+};
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int DP>
+struct BwdSmem {
+  static constexpr int kOperand = kT * DP * 2;       // K, V, Q, dO tiles
+  static constexpr int kPanel = kT * 128;            // one 64-column swizzled panel
+  static constexpr int kPds = kT * kT * 2;           // P, dS tiles
+  static constexpr int kK = 0, kV = kOperand, kQ = 2 * kOperand, kDO = 3 * kOperand;
+  static constexpr int kP = 4 * kOperand, kDS = kP + kPds;
+  static constexpr int kBarOffset = kDS + kPds;
+  static constexpr int kNumBars = 6;
+  static constexpr int kBytes = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kAlloc = kBytes + 1024;
+};
+
+template <typename T, int DP>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+           const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+           const BwdParams p) {
+  using L = BwdSmem<DP>;
+  constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  constexpr uint32_t kIdSS = idesc_f16(kFmt, false, kT, kT);           // S, dP: A, B K-major
+  constexpr uint32_t kIdTT = idesc_f16(kFmt, true, kT, DP, true);      // dV, dK: A, B MN-major
+  constexpr uint32_t kIdDQ = idesc_f16(kFmt, true, kT, DP, false);     // dQ: A K-major, B MN-major
+  constexpr int kPanels = DP / 64;
+
+  const int jt = blockIdx.x;                 // key tile
+  const int hk = blockIdx.y, b = blockIdx.z;
+  int seq_start = 0, len = p.seqlen, bcoord = b;
+  if (p.cu_seqlens) {
+    seq_start = p.cu_seqlens[b];
+    len = p.cu_seqlens[b + 1] - seq_start;
+    bcoord = 0;
+  }
+  const int kv0 = jt * kT;
+  if (kv0 >= len) return;
+  const int n_qtiles = (len + kT - 1) / kT;
+  const int i_first = p.causal ? jt : 0;     // first query tile that sees this key tile
+  const int n_iter = (n_qtiles - i_first) * p.group;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  const uint32_t bars = sbase + L::kBarOffset;
+  const uint32_t bar_kv = bars, bar_load = bars + 8, bar_sdp = bars + 16, bar_pds = bars + 24,
+                 bar_dq = bars + 32, bar_free = bars + 40;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kBarOffset + L::kNumBars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kBarOffset + L::kNumBars * 8 + 4);
+
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_kv, 1);
+    mbar_init(bar_load, 1);
+    mbar_init(bar_sdp, 1);
+    mbar_init(bar_pds, kT);
+    mbar_init(bar_dq, 1);
+    mbar_init(bar_free, kT);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tDP = tmem + 128, tDK = tmem + 256, tDV = tmem + 384;
+
+  if (warp == 4) {
+    // ============================================ control warp: TMA + MMA issue
+    const uint32_t issue = elect_one() ? 1u : 0u;
+    if (issue) {
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
+      mbar_expect_tx(bar_kv, 2 * L::kOperand);
+      for (int pn = 0; pn < kPanels; ++pn) {
+        tma_load_4d(sbase + L::kK + pn * L::kPanel, &tmap_k, bar_kv, 64 * pn, seq_start + kv0, hk, bcoord);
+        tma_load_4d(sbase + L::kV + pn * L::kPanel, &tmap_v, bar_kv, 64 * pn, seq_start + kv0, hk, bcoord);
+      }
+    }
+    __syncwarp();
+    const uint64_t d_q = smem_desc_sw128(sbase + L::kQ, 16, 1024);
+    const uint64_t d_k = smem_desc_sw128(sbase + L::kK, 16, 1024);
+    const uint64_t d_v = smem_desc_sw128(sbase + L::kV, 16, 1024);
+    const uint64_t d_do = smem_desc_sw128(sbase + L::kDO, 16, 1024);
+    const uint64_t d_p_mn = smem_desc_sw128(sbase + L::kP, L::kPanel, 1024);     // [q][k] read with M = k
+    const uint64_t d_ds_mn = smem_desc_sw128(sbase + L::kDS, L::kPanel, 1024);
+    const uint64_t d_ds_k = smem_desc_sw128(sbase + L::kDS, 16, 1024);           // same bytes, M = q
+    const uint64_t d_do_mn = smem_desc_sw128(sbase + L::kDO, L::kPanel, 1024);   // [q][d] read with K = q
+    const uint64_t d_q_mn = smem_desc_sw128(sbase + L::kQ, L::kPanel, 1024);
+    const uint64_t d_k_mn = smem_desc_sw128(sbase + L::kK, L::kPanel, 1024);     // [k][d] read with K = k
+    for (int it = 0; it < n_iter; ++it) {
+      const int g = it % p.group, i = i_first + it / p.group;
+      const int hq = hk * p.group + g;
+      // the previous pair's P, dS, Q, dO and the S / dP / dQ columns are free again
+      if (it > 0) mbar_wait(bar_free, (it - 1) & 1, abort_flag);
+      if (issue) {
+        mbar_expect_tx(bar_load, 2 * L::kOperand);
+        for (int pn = 0; pn < kPanels; ++pn) {
+          tma_load_4d(sbase + L::kQ + pn * L::kPanel, &tmap_q, bar_load, 64 * pn, seq_start + i * kT, hq, bcoord);
+          tma_load_4d(sbase + L::kDO + pn * L::kPanel, &tmap_do, bar_load, 64 * pn, seq_start + i * kT, hq, bcoord);
+        }
+      }
+      __syncwarp();
+      if (it == 0) mbar_wait(bar_kv, 0, abort_flag);
+      mbar_wait(bar_load, it & 1, abort_flag);
+      tc_fence_after();
+      // S = Q K^T, dP = dO V^T
+#pragma unroll
+      for (int ks = 0; ks < DP / 16; ++ks) {
+        const uint64_t off = (uint64_t)(((ks / 4) * L::kPanel + (ks % 4) * 32) >> 4);
+        mma_ss(tS, d_q + off, d_k + off, kIdSS, ks > 0, issue);
+      }
+#pragma unroll
+      for (int ks = 0; ks < DP / 16; ++ks) {
+        const uint64_t off = (uint64_t)(((ks / 4) * L::kPanel + (ks % 4) * 32) >> 4);
+        mma_ss(tDP, d_do + off, d_v + off, kIdSS, ks > 0, issue);
+      }
+      mma_commit(bar_sdp, issue);
+      // wait for P and dS in shared memory
+      mbar_wait(bar_pds, it & 1, abort_flag);
+      tc_fence_after();
+      const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+      for (int ks = 0; ks < kT / 16; ++ks) {   // contraction over the 128 queries
+        const uint64_t off = (uint64_t)((ks * 2048) >> 4);
+        mma_ss(tDV, d_p_mn + off, d_do_mn + off, kIdTT, ks > 0 ? 1u : acc, issue);
+      }
+#pragma unroll
+      for (int ks = 0; ks < kT / 16; ++ks) {
+        const uint64_t off = (uint64_t)((ks * 2048) >> 4);
+        mma_ss(tDK, d_ds_mn + off, d_q_mn + off, kIdTT, ks > 0 ? 1u : acc, issue);
+      }
+#pragma unroll
+      for (int ks = 0; ks < kT / 16; ++ks) {   // contraction over the 128 keys
+        const uint64_t offa = (uint64_t)(((ks / 4) * L::kPanel + (ks % 4) * 32) >> 4);
+        const uint64_t offb = (uint64_t)((ks * 2048) >> 4);
+        mma_ss(tS, d_ds_k + offa, d_k_mn + offb, kIdDQ, ks > 0, issue);
+      }
+      mma_commit(bar_dq, issue);
+    }
+  } else {
+    // ============================================ compute warps: one thread per row
+    const int row = threadIdx.x;                         // query row in the tile / key row in the epilogue
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    uint8_t* sP = sgen + L::kP;
+    uint8_t* sDS = sgen + L::kDS;
+    for (int it = 0; it < n_iter; ++it) {
+      const int g = it % p.group, i = i_first + it / p.group;
+      const int hq = hk * p.group + g;
+      const int qi = i * kT + row;
+      const bool row_ok = qi < len;
+      const long long tok = (long long)seq_start + qi;
+      float lse2 = 0.f, dsum = 0.f;
+      bool live = false;
+      if (row_ok) {
+        const float l = p.lse[(p.cu_seqlens ? 0 : (long long)b * p.lse_sb) + tok * p.lse_st + (long long)hq * p.lse_sh];
+        lse2 = p.lse_base2 ? l : l * 1.4426950408889634f;
+        live = l != -INFINITY;
+        const long long tl = p.cu_seqlens ? tok : (long long)b * p.seqlen + qi;
+        dsum = p.dvec[tl * p.heads_q + hq];
+      }
+      mbar_wait(bar_sdp, it & 1, abort_flag);
+      tc_fence_after();
+      // visible keys of this row inside the tile: columns [0, lim)
+      int lim = live ? min(kT, len - kv0) : 0;
+      if (p.causal) lim = min(lim, qi - kv0 + 1);
+#pragma unroll
+      for (int cc = 0; cc < kT / 32; ++cc) {
+        uint32_t sr[32], dr[32];
+        tmem_ld32(tS + lane_off + 32 * cc, sr);
+        tmem_ld32(tDP + lane_off + 32 * cc, dr);
+        tmem_wait_ld();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+          float p0 = ex2f(fmaf(__uint_as_float(sr[x]), p.scale_log2, -lse2));
+          float p1 = ex2f(fmaf(__uint_as_float(sr[x + 1]), p.scale_log2, -lse2));
+          if (32 * cc + x >= lim) p0 = 0.f;
+          if (32 * cc + x + 1 >= lim) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(dr[x]) - dsum);
+          const float d1 = p1 * (__uint_as_float(dr[x + 1]) - dsum);
+          pp[x / 2] = pack2<T>(p0, p1);
+          dd[x / 2] = pack2<T>(d0, d1);
+        }
+        // row `row` of a [128 q][128 k] tile, two 64-column panels, 128-byte swizzle
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int chunk = 4 * cc + ch;                       // 16-byte chunk of the 256-byte row
+          const uint32_t off = (chunk >> 3) * L::kPanel + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
+          *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[4 * ch], dd[4 * ch + 1], dd[4 * ch + 2], dd[4 * ch + 3]);
+        }
+      }
+      fence_proxy_async();       // generic-proxy writes -> visible to the tensor core's reads
+      tc_fence_before();
+      mbar_arrive(bar_pds);
+      // dQ tile of this pair -> fp32 accumulator
+      mbar_wait(bar_dq, it & 1, abort_flag);
+      tc_fence_after();
+      const long long tl = p.cu_seqlens ? tok : (long long)b * p.seqlen + qi;
+      float* qacc = p.dq_acc + (tl * p.heads_q + hq) * DP;
+#pragma unroll
+      for (int cc = 0; cc < DP / 32; ++cc) {
+        uint32_t qr[32];
+        tmem_ld32(tS + lane_off + 32 * cc, qr);
+        tmem_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int x = 0; x < 32; x += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(qacc + 32 * cc + x),
+                         "f"(__uint_as_float(qr[x]) * p.scale), "f"(__uint_as_float(qr[x + 1]) * p.scale),
+                         "f"(__uint_as_float(qr[x + 2]) * p.scale), "f"(__uint_as_float(qr[x + 3]) * p.scale)
+                         : "memory");
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_free);
+    }
+    // ---- dK, dV of this key tile (every product has completed: the last bar_dq was waited)
+    // (tcgen05.ld is warp-collective: every thread runs the loads, only the
+    // stores depend on the row being a real key)
+    const int kj = kv0 + row;
+    const bool key_ok = kj < len;
+    const long long ktok = (long long)seq_start + (key_ok ? kj : 0);
+    T* dkrow = (T*)p.dk + (p.cu_seqlens ? 0 : (long long)b * p.dk_sb) + ktok * p.dk_st + (long long)hk * p.dk_sh;
+    T* dvrow = (T*)p.dv + (p.cu_seqlens ? 0 : (long long)b * p.dv_sb) + ktok * p.dv_st + (long long)hk * p.dv_sh;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const float sc = which ? 1.f : p.scale;
+      T* dst = which ? dvrow : dkrow;
+#pragma unroll
+      for (int cc = 0; cc < DP / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld32((which ? tDV : tDK) + lane_off + 32 * cc, r);
+        tmem_wait_ld();
+        if (key_ok && 32 * cc < p.head_dim) {
+#pragma unroll
+          for (int x = 0; x < 32; x += 8) {
+            uint4 pk;
+            pk.x = pack2<T>(__uint_as_float(r[x]) * sc, __uint_as_float(r[x + 1]) * sc);
+            pk.y = pack2<T>(__uint_as_float(r[x + 2]) * sc, __uint_as_float(r[x + 3]) * sc);
+            pk.z = pack2<T>(__uint_as_float(r[x + 4]) * sc, __uint_as_float(r[x + 5]) * sc);
+            pk.w = pack2<T>(__uint_as_float(r[x + 6]) * sc, __uint_as_float(r[x + 7]) * sc);
+            *reinterpret_cast<uint4*>(dst + 32 * cc + x) = pk;
+          }
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && p.status_word) atomicExch(p.status_word, 1);
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// D[t, h] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head).
+template <typename T>
+__global__ void bwd_rowsum_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ dvec,
+                                  long long o_sb, long long o_st, long long o_sh, long long do_sb,
+                                  long long do_st, long long do_sh, int tokens_per_batch, int heads, int D,
+                                  long long total) {
+  const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (idx >= total) return;
+  const int lane = threadIdx.x & 31;
+  const int hq = (int)(idx % heads);
+  const long long tl = idx / heads;
+  const long long bb = tl / tokens_per_batch, tt = tl % tokens_per_batch;
+  const T* orow = o + bb * o_sb + tt * o_st + (long long)hq * o_sh;
+  const T* drow = d_o + bb * do_sb + tt * do_st + (long long)hq * do_sh;
+  float s = 0.f;
+  for (int d = lane; d < D; d += 32) s += (float)orow[d] * (float)drow[d];
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(0xffffffffu, s, k);
+  if (lane == 0) dvec[idx] = s;
+}
+
+// dq[t, h, :D] = T(dq_acc[t, h, :D])
+template <typename T>
+__global__ void bwd_convert_dq_kernel(const float* __restrict__ acc, T* __restrict__ dq, long long dq_sb,
+                                      long long dq_st, long long dq_sh, int tokens_per_batch, int heads, int D,
+                                      int DP, long long total_rows) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one thread per 8 elements
+  const int per_row = DP / 8;
+  const long long r = idx / per_row;
+  const int c = (int)(idx % per_row) * 8;
+  if (r >= total_rows || c >= D) return;
+  const int hq = (int)(r % heads);
+  const long long tl = r / heads;
+  const long long bb = tl / tokens_per_batch, tt = tl % tokens_per_batch;
+  const float4 a = *reinterpret_cast<const float4*>(acc + r * DP + c);
+  const float4 bq = *reinterpret_cast<const float4*>(acc + r * DP + c + 4);
+  uint4 pk;
+  pk.x = pack2<T>(a.x, a.y); pk.y = pack2<T>(a.z, a.w);
+  pk.z = pack2<T>(bq.x, bq.y); pk.w = pack2<T>(bq.z, bq.w);
+  *reinterpret_cast<uint4*>(dq + bb * dq_sb + tt * dq_st + (long long)hq * dq_sh + c) = pk;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return (EncodeTiledFn)f;
+  }();
+  return fn;
+}
+
+bool make_tmap(CUtensorMap* m, int dtype, const void* base, int D, long long tokens, int heads, int batch,
+               long long st, long long sh, long long sb) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)tokens, (cuuint64_t)heads, (cuuint64_t)batch};
+  if (batch <= 1 || sb <= 0) sb = st * tokens;
+  cuuint64_t strides[3] = {(cuuint64_t)st * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)kT, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(m, dtype == B200ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int dpad(int d) { return d <= 64 ? 64 : 128; }
+
+long long total_rows(const b200attn_prefill_bwd_args* a) {
+  const long long tokens = a->cu_seqlens ? a->total_tokens : (long long)a->batch * a->seqlen;
+  return tokens * a->heads_q;
+}
+
+int validate_bwd(const b200attn_prefill_bwd_args* a) {
+  if (!a || !a->q || !a->k || !a->v || !a->o || !a->d_o || !a->lse || !a->dq || !a->dk || !a->dv)
+    return B200ATTN_ERR_NULL;
+  if (a->dtype != B200ATTN_F16 && a->dtype != B200ATTN_BF16) return B200ATTN_ERR_DTYPE;
+  if (a->head_dim != 32 && a->head_dim != 64 && a->head_dim != 96 && a->head_dim != 128)
+    return B200ATTN_ERR_HEAD_DIM;
+  if (a->batch <= 0 || a->heads_q <= 0 || a->heads_kv <= 0) return B200ATTN_ERR_SHAPE;
+  if (a->heads_q % a->heads_kv != 0) return B200ATTN_ERR_GQA;
+  if (a->cu_seqlens) {
+    if (a->max_seqlen < 0 || a->total_tokens <= 0) return B200ATTN_ERR_SHAPE;
+  } else if (a->seqlen <= 0) {
+    return B200ATTN_ERR_SHAPE;
+  }
+  const void* ptrs[8] = {a->q, a->k, a->v, a->o, a->d_o, a->dq, a->dk, a->dv};
+  for (const void* ptr : ptrs)
+    if ((uintptr_t)ptr & 15) return B200ATTN_ERR_ALIGN;
+  const long long strides[24] = {
+      a->q_stride_b, a->q_stride_t, a->q_stride_h, a->k_stride_b, a->k_stride_t, a->k_stride_h,
+      a->v_stride_b, a->v_stride_t, a->v_stride_h, a->o_stride_b, a->o_stride_t, a->o_stride_h,
+      a->do_stride_b, a->do_stride_t, a->do_stride_h, a->dq_stride_b, a->dq_stride_t, a->dq_stride_h,
+      a->dk_stride_b, a->dk_stride_t, a->dk_stride_h, a->dv_stride_b, a->dv_stride_t, a->dv_stride_h};
+  for (long long s : strides)
+    if (s % 8 != 0 || s < 0) return B200ATTN_ERR_STRIDE;
+  if (!(a->softmax_scale > 0.f)) return B200ATTN_ERR_SHAPE;
+  if (a->heads_kv > 65535 || a->batch > 65535) return B200ATTN_ERR_TOO_LARGE;
+  return B200ATTN_OK;
+}
+
+template <typename T, int DP>
+int launch_bwd(const b200attn_prefill_bwd_args* a, const BwdParams& p, cudaStream_t stream) {
+  using L = BwdSmem<DP>;
+  const long long tokens = a->cu_seqlens ? a->total_tokens : a->seqlen;
+  const int tb = a->cu_seqlens ? 1 : a->batch;
+  CUtensorMap tq, tk, tv, tdo;
+  if (!make_tmap(&tq, a->dtype, a->q, a->head_dim, tokens, a->heads_q, tb, a->q_stride_t, a->q_stride_h, a->q_stride_b) ||
+      !make_tmap(&tk, a->dtype, a->k, a->head_dim, tokens, a->heads_kv, tb, a->k_stride_t, a->k_stride_h, a->k_stride_b) ||
+      !make_tmap(&tv, a->dtype, a->v, a->head_dim, tokens, a->heads_kv, tb, a->v_stride_t, a->v_stride_h, a->v_stride_b) ||
+      !make_tmap(&tdo, a->dtype, a->d_o, a->head_dim, tokens, a->heads_q, tb, a->do_stride_t, a->do_stride_h, a->do_stride_b))
+    return B200ATTN_ERR_CUDA;
+  auto kern = bwd_kernel<T, DP>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
+      return B200ATTN_ERR_CUDA;
+    attr_set = true;
+  }
+  const long long rows = total_rows(a);
+  const int tpb = a->cu_seqlens ? (int)a->total_tokens : a->seqlen;   // tokens per batch entry of the dense index
+  // 1. D = rowsum(dO o O)
+  {
+    const int warps_per_block = 8;
+    const long long blocks = (rows + warps_per_block - 1) / warps_per_block;
+    bwd_rowsum_kernel<T><<<(unsigned)blocks, warps_per_block * 32, 0, stream>>>(
+        (const T*)a->o, (const T*)a->d_o, const_cast<float*>(p.dvec), a->cu_seqlens ? 0 : a->o_stride_b,
+        a->o_stride_t, a->o_stride_h, a->cu_seqlens ? 0 : a->do_stride_b, a->do_stride_t, a->do_stride_h, tpb,
+        a->heads_q, a->head_dim, rows);
+  }
+  // 2. main kernel (dq accumulator zeroed first)
+  if (cudaMemsetAsync(p.dq_acc, 0, (size_t)rows * DP * 4, stream) != cudaSuccess) return B200ATTN_ERR_CUDA;
+  dim3 grid(p.n_kvtiles, a->heads_kv, a->batch);
+  kern<<<grid, kBwdThreads, L::kAlloc, stream>>>(tq, tk, tv, tdo, p);
+  // 3. dq accumulator -> dq
+  {
+    const long long items = rows * (DP / 8);
+    bwd_convert_dq_kernel<T><<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(
+        p.dq_acc, (T*)a->dq, a->cu_seqlens ? 0 : a->dq_stride_b, a->dq_stride_t, a->dq_stride_h, tpb,
+        a->heads_q, a->head_dim, DP, rows);
+  }
+  set_launch_count(3);
+  return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+}
+
+}  // namespace
+
+size_t prefill_bwd_workspace_bytes(const b200attn_prefill_bwd_args* a) {
+  if (!a || a->heads_q <= 0) return 0;
+  const long long rows = total_rows(a);
+  if (rows <= 0) return 0;
+  return (size_t)rows * dpad(a->head_dim) * 4 + (size_t)rows * 4;
+}
+
+int prefill_bwd(const b200attn_prefill_bwd_args* a, cudaStream_t stream) {
+  int st = validate_bwd(a);
+  if (st != B200ATTN_OK) return st;
+  const size_t need = prefill_bwd_workspace_bytes(a);
+  if (!a->workspace || a->workspace_bytes < need) return B200ATTN_ERR_WORKSPACE;
+  if ((uintptr_t)a->workspace & 15) return B200ATTN_ERR_ALIGN;
+  const long long rows = total_rows(a);
+  const int DP = dpad(a->head_dim);
+  BwdParams p;
+  p.lse = a->lse;
+  p.dq_acc = (float*)a->workspace;
+  p.dvec = p.dq_acc + rows * DP;
+  p.dk = a->dk; p.dv = a->dv;
+  p.cu_seqlens = a->cu_seqlens;
+  p.lse_sb = a->lse_stride_b; p.lse_st = a->lse_stride_t; p.lse_sh = a->lse_stride_h;
+  p.dk_sb = a->dk_stride_b; p.dk_st = a->dk_stride_t; p.dk_sh = a->dk_stride_h;
+  p.dv_sb = a->dv_stride_b; p.dv_st = a->dv_stride_t; p.dv_sh = a->dv_stride_h;
+  p.batch = a->batch; p.heads_q = a->heads_q; p.heads_kv = a->heads_kv;
+  p.group = a->heads_q / a->heads_kv; p.head_dim = a->head_dim;
+  p.seqlen = a->seqlen;
+  const int maxlen = a->cu_seqlens ? a->max_seqlen : a->seqlen;
+  p.n_kvtiles = (maxlen + kT - 1) / kT;
+  if (p.n_kvtiles <= 0) return B200ATTN_OK;
+  p.causal = a->causal ? 1 : 0;
+  p.scale = a->softmax_scale * (a->scale_has_log2e ? 0.6931471805599453f : 1.f);
+  p.scale_log2 = a->softmax_scale * (a->scale_has_log2e ? 1.f : 1.4426950408889634f);
+  p.lse_base2 = a->lse_base2;
+  p.status_word = a->status_word;
+  const bool dp64 = DP == 64;
+  if (a->dtype == B200ATTN_F16)
+    return dp64 ? launch_bwd<__half, 64>(a, p, stream) : launch_bwd<__half, 128>(a, p, stream);
+  return dp64 ? launch_bwd<__nv_bfloat16, 64>(a, p, stream) : launch_bwd<__nv_bfloat16, 128>(a, p, stream);
+}
+
+}  // namespace b200attn

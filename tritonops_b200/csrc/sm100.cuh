@@ -162,9 +162,10 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_
 // Instruction descriptor for kind::f16: fp32 accumulate, A and B both `fmt`
 // (0 = f16, 1 = bf16), A K-major, B K-major or MN-major, M x N tile.
 __host__ __device__ constexpr uint32_t idesc_f16(uint32_t fmt, bool b_mn_major, uint32_t M,
-                                                 uint32_t N) {
+                                                 uint32_t N, bool a_mn_major = false) {
   return (1u << 4)                          // D format: f32
          | (fmt << 7) | (fmt << 10)         // A, B formats
+         | ((a_mn_major ? 1u : 0u) << 15)   // A major
          | ((b_mn_major ? 1u : 0u) << 16)   // B major
          | ((N >> 3) << 17) | ((M >> 4) << 24);
 }

@@ -18,9 +18,18 @@ def flash_attn_triton_fwd(q, k, v, cu_seq_lens, sm_scale, causal=True, max_seqle
                        scale_has_log2e=True, causal=causal, lse_base2=True)
 
 
+def flash_attn_triton_bwd(q, k, v, o, do, lse, cu_seq_lens, sm_scale, causal=True, max_seqlen=None):
+    """Same contract as the reference launcher (flash_attn_triton.py:661-813):
+    ``lse`` is the base-2 LSE the forward returned, ``sm_scale`` contains
+    log2(e); returns (dq, dk, dv) with dk / dv already summed over the query
+    heads of each GQA group (:813)."""
+    return ops.prefill_bwd(q, k, v, o, do, lse, cu_seqlens=cu_seq_lens, max_seqlen=max_seqlen,
+                           scale=sm_scale, scale_has_log2e=True, causal=causal, lse_base2=True)
+
+
 class flash_attn_triton(torch.autograd.Function):
     """``flash_attn_triton.apply(q, k, v, cu_seq_lens) -> o`` as in the reference
-    (flash_attn_triton.py:816-846).  Forward only: backward raises."""
+    (flash_attn_triton.py:816-874), forward and backward."""
 
     @staticmethod
     def forward(ctx, q, k, v, cu_seq_lens):
@@ -32,8 +41,9 @@ class flash_attn_triton(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do):
-        raise NotImplementedError(
-            "tritonops_b200 implements the forward pass of flash_attn_triton only")
+        q, k, v, o, lse, cu_seq_lens = ctx.saved_tensors
+        dq, dk, dv = flash_attn_triton_bwd(q, k, v, o, do, lse, cu_seq_lens, ctx.sm_scale)
+        return dq, dk, dv, None
 
 
 def flash_attention(q, k, v, cu_seq_lens=None, causal=True, softmax_scale=None,

@@ -11,7 +11,7 @@ import torch
 from torch import Tensor
 
 from . import _lib
-from ._lib import BLOCK_LIST, DENSE, WINDOW, DecodeArgs, PrefillArgs
+from ._lib import BLOCK_LIST, DENSE, WINDOW, DecodeArgs, PrefillArgs, PrefillBwdArgs
 
 LOG2E = 1.4426950408889634
 _DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
@@ -197,3 +197,68 @@ def prefill(q, k, v, *, cu_seqlens=None, max_seqlen=None, scale=None, scale_has_
                        bool(causal), bool(lse_base2), int(sparsity), int(window_local),
                        int(window_global), _i32(block_idx, q.device), _i32(block_cnt, q.device),
                        int(block_size))
+
+
+# --------------------------------------------------------------------------
+# prefill backward
+# --------------------------------------------------------------------------
+@torch.library.custom_op("b200attn::prefill_bwd", mutates_args=())
+def _prefill_bwd_op(q: Tensor, k: Tensor, v: Tensor, o: Tensor, d_o: Tensor, lse: Tensor,
+                    cu_seqlens: Optional[Tensor], max_seqlen: int, scale: float,
+                    scale_has_log2e: bool, causal: bool, lse_base2: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    _need_cuda(q, k, v, o, d_o, lse, cu_seqlens)
+    if q.dtype not in _DT or any(t.dtype != q.dtype for t in (k, v, o, d_o)):
+        raise ValueError("b200attn: q, k, v, o, do must share dtype float16 or bfloat16")
+    q, k, v, o, d_o = (_rowmajor16(t) for t in (q, k, v, o, d_o))
+    lse = lse.contiguous() if lse.dtype == torch.float32 else lse.float().contiguous()
+    Bt, T, Hq, D = q.shape
+    Hkv = k.shape[2]
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dq, dk, dv = dq.contiguous(), dk.contiguous(), dv.contiguous()
+    a = PrefillBwdArgs()
+    a.q, a.k, a.v, a.o, a.d_o, a.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(d_o), _ptr(lse)
+    a.dq, a.dk, a.dv = _ptr(dq), _ptr(dk), _ptr(dv)
+    a.dtype, a.heads_q, a.heads_kv, a.head_dim = _DT[q.dtype], Hq, Hkv, D
+    if cu_seqlens is not None:
+        if Bt != 1:
+            raise ValueError("packed varlen tensors must have a leading dimension of 1")
+        a.batch, a.cu_seqlens = cu_seqlens.numel() - 1, _ptr(cu_seqlens)
+        a.max_seqlen, a.total_tokens, a.seqlen = max_seqlen, T, 0
+    else:
+        a.batch, a.seqlen, a.max_seqlen, a.total_tokens = Bt, T, T, T
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", o), ("do", d_o), ("dq", dq), ("dk", dk),
+                    ("dv", dv), ("lse", lse)):
+        setattr(a, f"{name}_stride_b", t.stride(0))
+        setattr(a, f"{name}_stride_t", t.stride(1))
+        setattr(a, f"{name}_stride_h", t.stride(2))
+    a.softmax_scale, a.scale_has_log2e = scale, int(scale_has_log2e)
+    a.causal, a.lse_base2 = int(causal), int(lse_base2)
+    L = _lib.lib()
+    need = L.b200attn_prefill_bwd_workspace_bytes(C.byref(a))
+    ws = torch.empty(max(need, 16), device=q.device, dtype=torch.uint8)
+    a.workspace, a.workspace_bytes = _ptr(ws), ws.numel()
+    with torch.cuda.device(q.device):
+        _lib.check(L.b200attn_prefill_bwd(C.byref(a), _stream(q)))
+    _count()
+    return dq, dk, dv
+
+
+@_prefill_bwd_op.register_fake
+def _(q, k, v, o, d_o, lse, cu_seqlens, max_seqlen, scale, scale_has_log2e, causal, lse_base2):
+    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
+def prefill_bwd(q, k, v, o, d_o, lse, *, cu_seqlens=None, max_seqlen=None, scale=None,
+                scale_has_log2e=False, causal=True, lse_base2=False):
+    """Gradients (dq, dk, dv) of the dense prefill; see b200attn_prefill_bwd in include/b200attn.h.
+    `o`, `lse` are the forward's outputs (lse in the form given by `lse_base2`)."""
+    cu = _i32(cu_seqlens, q.device)
+    if scale is None:
+        scale, scale_has_log2e = q.shape[-1] ** -0.5, False
+    if max_seqlen is None:
+        if cu is not None:
+            max_seqlen = int((cu[1:] - cu[:-1]).max().item()) if cu.numel() > 1 else 0
+        else:
+            max_seqlen = q.shape[1]
+    return _prefill_bwd_op(q, k, v, o, d_o, lse, cu, int(max_seqlen), float(scale),
+                           bool(scale_has_log2e), bool(causal), bool(lse_base2))
