@@ -244,6 +244,24 @@ def run_ours(args, rank, world, local_rank):
         del w3
     except Exception as e:  # keep the headline even if a secondary config fails
         other["cfg3_gqa_decode"] = {"error": repr(e)}
+    # ---------------- config 2 backward (dQ, dK, dV; 2.5x the forward FLOPs)
+    try:
+        o2, lse2 = flash_attn_triton_fwd(w.q, w.k, w.v, w.cu_seqlens, sm_scale, max_seqlen=w.max_seqlen)
+        do2 = torch.randn(w.q.shape, device=dev, dtype=torch.float32).to(w.q.dtype)
+        fb = lambda: ops.prefill_bwd(w.q, w.k, w.v, o2, do2, lse2, cu_seqlens=w.cu_seqlens,
+                                     max_seqlen=w.max_seqlen, scale=sm_scale, scale_has_log2e=True,
+                                     lse_base2=True)
+        msb = reduce_max(time_steps(fb, max(args.steps // 2, 5), 3, sync, barrier))
+        tfb = 2.5 * w.flops / msb / 1e9
+        other["cfg2_backward"] = {
+            "value": tfb * world, "unit": "TFLOP/s", "ms_per_step": msb,
+            "roofline": {"bound": "tensor", "achieved": tfb, "peak": pk["tflops"], "unit": "TFLOP/s",
+                         "frac": tfb / pk["tflops"], "traffic": None},
+            "config": {"workload": "backward of cfg2 (dense causal bf16 B=4 H=32 S=4096 D=128): dQ, dK, dV",
+                       "flops": "2.5 x the causal forward count (five products instead of two)"}}
+        del o2, lse2, do2
+    except Exception as e:
+        other["cfg2_backward"] = {"error": repr(e)}
     # ---------------- config 4: block-sparse causal prefill (tensor bound, gathered KV blocks)
     try:
         from tritonops_b200.flash_attn_triton.flash_attn_sparse_attn_triton import flash_attn_block_sparse
