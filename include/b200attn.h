@@ -226,6 +226,41 @@ size_t b200attn_prefill_bwd_workspace_bytes(const b200attn_prefill_bwd_args* arg
  * its kernels (:184-592). */
 int b200attn_prefill_bwd(const b200attn_prefill_bwd_args* args, b200attn_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * KV-cache glue (16-bit elements, head_dim a multiple of 8).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const void* packed;          /* [total_tokens, heads, head_dim] rows of all sequences */
+  void* cache;                 /* [batch, capacity, heads, head_dim] */
+  const int32_t* cu_seqlens;   /* int32 [batch+1] */
+  int32_t batch, heads, head_dim, capacity;
+  int64_t packed_stride_t, packed_stride_h;
+  int64_t cache_stride_b, cache_stride_t, cache_stride_h;
+  int32_t zero_pad;            /* 1: rows t >= len_b of the cache are set to zero */
+} b200attn_kv_pack_args;
+
+/* Packed varlen K (or V) rows -> padded cache: cache[b, t] = packed[cu[b] + t]
+ * for t < len_b.  Replaces the Python copy loops of the reference's decoding
+ * tests (flash_attn_triton/flash_attn_decoding.py:404-425). */
+int b200attn_kv_pack_to_cache(const b200attn_kv_pack_args* args, b200attn_stream_t stream);
+
+typedef struct {
+  const void* new_k;           /* [batch, heads, head_dim] the token to append */
+  const void* new_v;
+  void* k_cache;               /* [batch, capacity, heads, head_dim] */
+  void* v_cache;
+  const int32_t* seqlens;      /* int32 [batch]: current lengths = write positions */
+  int32_t batch, heads, head_dim, capacity;
+  int64_t new_stride_b, new_stride_h;
+  int64_t cache_stride_b, cache_stride_t, cache_stride_h;
+} b200attn_kv_append_args;
+
+/* One decoding step's new K/V rows written at position len_b of each sequence
+ * (sequences already at capacity are skipped).  No counterpart function in the
+ * reference, whose tests rebuild the whole cache instead
+ * (flash_attn_triton/flash_attn_decoding_sparse.py:445-466). */
+int b200attn_kv_append(const b200attn_kv_append_args* args, b200attn_stream_t stream);
+
 /* Prefill needs no scratch; kept so callers can size buffers uniformly. */
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args* args);
 

@@ -60,6 +60,21 @@ class PrefillBwdArgs(C.Structure):
     ]
 
 
+class KvPackArgs(C.Structure):
+    _fields_ = [("packed", vp), ("cache", vp), ("cu_seqlens", vp),
+                ("batch", i32), ("heads", i32), ("head_dim", i32), ("capacity", i32),
+                ("packed_stride_t", i64), ("packed_stride_h", i64),
+                ("cache_stride_b", i64), ("cache_stride_t", i64), ("cache_stride_h", i64),
+                ("zero_pad", i32)]
+
+
+class KvAppendArgs(C.Structure):
+    _fields_ = [("new_k", vp), ("new_v", vp), ("k_cache", vp), ("v_cache", vp), ("seqlens", vp),
+                ("batch", i32), ("heads", i32), ("head_dim", i32), ("capacity", i32),
+                ("new_stride_b", i64), ("new_stride_h", i64),
+                ("cache_stride_b", i64), ("cache_stride_t", i64), ("cache_stride_h", i64)]
+
+
 # every symbol include/b200attn.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "b200attn_abi_version": (C.c_int, []),
@@ -74,6 +89,8 @@ SYMBOLS = {
     "b200attn_decode_fwd_noalloc": (C.c_int, [C.POINTER(DecodeArgs), vp]),
     "b200attn_prefill_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(PrefillBwdArgs)]),
     "b200attn_prefill_bwd": (C.c_int, [C.POINTER(PrefillBwdArgs), vp]),
+    "b200attn_kv_pack_to_cache": (C.c_int, [C.POINTER(KvPackArgs), vp]),
+    "b200attn_kv_append": (C.c_int, [C.POINTER(KvAppendArgs), vp]),
 }
 NOALLOC_SCRATCH_BYTES = 32 << 20
 

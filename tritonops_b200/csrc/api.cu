@@ -62,6 +62,16 @@ int b200attn_prefill_bwd(const b200attn_prefill_bwd_args* args, b200attn_stream_
   return prefill_bwd(args, (cudaStream_t)stream);
 }
 
+int b200attn_kv_pack_to_cache(const b200attn_kv_pack_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return kv_pack_to_cache(args, (cudaStream_t)stream);
+}
+
+int b200attn_kv_append(const b200attn_kv_append_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return kv_append(args, (cudaStream_t)stream);
+}
+
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args*) { return 0; }
 
 int b200attn_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream) {

@@ -20,6 +20,8 @@ int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream
 int decode_fwd_noalloc(const b200attn_decode_args* a, cudaStream_t stream);
 size_t prefill_bwd_workspace_bytes(const b200attn_prefill_bwd_args* a);
 int prefill_bwd(const b200attn_prefill_bwd_args* a, cudaStream_t stream);
+int kv_pack_to_cache(const b200attn_kv_pack_args* a, cudaStream_t stream);
+int kv_append(const b200attn_kv_append_args* a, cudaStream_t stream);
 
 // 16-byte read-only load that does not pollute L1 (data is used once).
 template <typename T>

@@ -11,7 +11,8 @@ import torch
 from torch import Tensor
 
 from . import _lib
-from ._lib import BLOCK_LIST, DENSE, WINDOW, DecodeArgs, PrefillArgs, PrefillBwdArgs
+from ._lib import (BLOCK_LIST, DENSE, WINDOW, DecodeArgs, KvAppendArgs, KvPackArgs, PrefillArgs,
+                   PrefillBwdArgs)
 
 LOG2E = 1.4426950408889634
 _DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
@@ -262,3 +263,49 @@ def prefill_bwd(q, k, v, o, d_o, lse, *, cu_seqlens=None, max_seqlen=None, scale
             max_seqlen = q.shape[1]
     return _prefill_bwd_op(q, k, v, o, d_o, lse, cu, int(max_seqlen), float(scale),
                            bool(scale_has_log2e), bool(causal), bool(lse_base2))
+
+
+# --------------------------------------------------------------------------
+# KV-cache glue
+# --------------------------------------------------------------------------
+def pack_kv_cache(packed: Tensor, cu_seqlens: Tensor, capacity: int, out: Optional[Tensor] = None,
+                  zero_pad: bool = True) -> Tensor:
+    """Packed rows [1, T, H, D] (or [T, H, D]) -> padded cache [B, capacity, H, D], the copy
+    the reference's decoding tests do in Python (flash_attn_decoding.py:404-425)."""
+    _need_cuda(packed, cu_seqlens, out)
+    if packed.dtype not in _DT:
+        raise ValueError("b200attn: packed rows must be float16 or bfloat16")
+    if packed.dim() == 4:
+        packed = packed[0]
+    packed = _rowmajor16(packed)
+    cu = _i32(cu_seqlens, packed.device)
+    B, (T, H, D) = cu.numel() - 1, packed.shape
+    if out is None:
+        out = torch.empty(B, capacity, H, D, device=packed.device, dtype=packed.dtype)
+    a = KvPackArgs()
+    a.packed, a.cache, a.cu_seqlens = _ptr(packed), _ptr(out), _ptr(cu)
+    a.batch, a.heads, a.head_dim, a.capacity = B, H, D, out.shape[1]
+    a.packed_stride_t, a.packed_stride_h = packed.stride(0), packed.stride(1)
+    a.cache_stride_b, a.cache_stride_t, a.cache_stride_h = out.stride(0), out.stride(1), out.stride(2)
+    a.zero_pad = int(zero_pad)
+    with torch.cuda.device(packed.device):
+        _lib.check(_lib.lib().b200attn_kv_pack_to_cache(C.byref(a), _stream(packed)))
+    _count()
+    return out
+
+
+def append_kv(k_cache: Tensor, v_cache: Tensor, new_k: Tensor, new_v: Tensor, seqlens: Tensor) -> None:
+    """In place: cache[b, seqlens[b]] = new[b] for K and V (one decoding step)."""
+    _need_cuda(k_cache, v_cache, new_k, new_v, seqlens)
+    if k_cache.stride() != v_cache.stride() or new_k.stride() != new_v.stride():
+        raise ValueError("b200attn: K and V caches (and new rows) must share their strides")
+    sl = _i32(seqlens, k_cache.device)
+    B, cap, H, D = k_cache.shape
+    a = KvAppendArgs()
+    a.new_k, a.new_v, a.k_cache, a.v_cache, a.seqlens = _ptr(new_k), _ptr(new_v), _ptr(k_cache), _ptr(v_cache), _ptr(sl)
+    a.batch, a.heads, a.head_dim, a.capacity = B, H, D, cap
+    a.new_stride_b, a.new_stride_h = new_k.stride(0), new_k.stride(1)
+    a.cache_stride_b, a.cache_stride_t, a.cache_stride_h = k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)
+    with torch.cuda.device(k_cache.device):
+        _lib.check(_lib.lib().b200attn_kv_append(C.byref(a), _stream(k_cache)))
+    _count()
