@@ -419,10 +419,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (!q_ready[t]) { mbar_wait(q_full(t), 0, abort_flag); tc_fence_after(); q_ready[t] = true; }
         const uint64_t da = dq0 + (uint64_t)((t * L::kQBytes) >> 4);
         const uint64_t db = dk0 + (uint64_t)((s * L::kStageBytes) >> 4);
-#pragma unroll
-        for (int ks = 0; ks < DP / 16; ++ks)
-          mma_ss(tS(t), da + (uint64_t)(((ks / 4) * L::kQPanel + (ks % 4) * 32) >> 4),
-                 db + (uint64_t)(((ks / 4) * L::kKvPanel + (ks % 4) * 32) >> 4), kIdescQK, ks > 0, issue);
+        static_assert(BN == 128, "the grouped issue assumes 16 KB panels");
+        if (DP == 128)
+          mma_ss_x8(tS(t), (uint32_t)da, (uint32_t)(da >> 32), (uint32_t)db, (uint32_t)(db >> 32), kIdescQK, issue);
+        else
+          mma_ss_x4(tS(t), (uint32_t)da, (uint32_t)(da >> 32), (uint32_t)db, (uint32_t)(db >> 32), kIdescQK, issue);
         mma_commit(s_full(t), issue);
         if (issue) TRACE(25 + t);
       };
@@ -431,11 +432,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         tc_fence_after();
         if (issue) TRACE(10 + t);
         const uint64_t db = dv0 + (uint64_t)((s * L::kStageBytes) >> 4);
-        const uint32_t acc = pv_cnt[t] > 0 ? 1u : 0u;
-#pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks)
-          mma_ts(tO(t), tS(t) + 8u * ks, db + (uint64_t)((ks * 2048) >> 4), kIdescPV,
-                 ks > 0 ? 1u : acc, issue);
+        mma_ts_x8(tO(t), tS(t), (uint32_t)db, (uint32_t)(db >> 32), kIdescPV, pv_cnt[t] > 0 ? 1u : 0u, issue);
         mma_commit(o_full(t), issue);
         if (issue) TRACE(20 + t);
         ++pv_cnt[t];

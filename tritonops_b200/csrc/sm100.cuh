@@ -193,6 +193,81 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(issue)
       : "memory");
 }
+// 8 back-to-back SS products (one 128-wide contraction in steps of 16): D = A B, the
+// first step overwrites D.  Descriptors are given as (low, high) words; a step only adds to
+// the address field in the low word.
+__device__ __forceinline__ void mma_ss_x8(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                           uint32_t b_hi, uint32_t idesc, uint32_t issue) {
+  asm volatile(
+      "{\n\t.reg .pred pi, pt, pf;\n\t.reg .b64 da, db;\n\t.reg .b32 la, lb;\n\t"
+      "setp.ne.b32 pi, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tsetp.ne.b32 pf, 0, 0;\n\t"
+      "add.u32 la, %1, 0;\n\tadd.u32 lb, %3, 0;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pf;\n\t"
+      "add.u32 la, %1, 2;\n\tadd.u32 lb, %3, 2;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "add.u32 la, %1, 4;\n\tadd.u32 lb, %3, 4;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "add.u32 la, %1, 6;\n\tadd.u32 lb, %3, 6;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "add.u32 la, %1, 1024;\n\tadd.u32 lb, %3, 1024;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "add.u32 la, %1, 1026;\n\tadd.u32 lb, %3, 1026;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "add.u32 la, %1, 1028;\n\tadd.u32 lb, %3, 1028;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "add.u32 la, %1, 1030;\n\tadd.u32 lb, %3, 1030;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(issue)
+      : "memory");
+}
+// 4 back-to-back SS products (one 128-wide contraction in steps of 16): D = A B, the
+// first step overwrites D.  Descriptors are given as (low, high) words; a step only adds to
+// the address field in the low word.
+__device__ __forceinline__ void mma_ss_x4(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                           uint32_t b_hi, uint32_t idesc, uint32_t issue) {
+  asm volatile(
+      "{\n\t.reg .pred pi, pt, pf;\n\t.reg .b64 da, db;\n\t.reg .b32 la, lb;\n\t"
+      "setp.ne.b32 pi, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tsetp.ne.b32 pf, 0, 0;\n\t"
+      "add.u32 la, %1, 0;\n\tadd.u32 lb, %3, 0;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pf;\n\t"
+      "add.u32 la, %1, 2;\n\tadd.u32 lb, %3, 2;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "add.u32 la, %1, 4;\n\tadd.u32 lb, %3, 4;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "add.u32 la, %1, 6;\n\tadd.u32 lb, %3, 6;\n\tmov.b64 da, {la, %2};\n\tmov.b64 db, {lb, %4};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(issue)
+      : "memory");
+}
+// 8 back-to-back TS products over 128 keys: D (+)= A[tmem] B[smem]; A advances by 8 TMEM
+// columns per step, B by 2048 bytes; the first step accumulates only if `accumulate`.
+__device__ __forceinline__ void mma_ts_x8(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                           uint32_t idesc, uint32_t accumulate, uint32_t issue) {
+  asm volatile(
+      "{\n\t.reg .pred pi, pt, pa;\n\t.reg .b64 db;\n\t.reg .b32 ta, lb;\n\t"
+      "setp.ne.b32 pi, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tsetp.ne.b32 pa, %5, 0;\n\t"
+      "add.u32 ta, %1, 0;\n\tadd.u32 lb, %2, 0;\n\tmov.b64 db, {lb, %3};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pa;\n\t"
+      "add.u32 ta, %1, 8;\n\tadd.u32 lb, %2, 128;\n\tmov.b64 db, {lb, %3};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
+      "add.u32 ta, %1, 16;\n\tadd.u32 lb, %2, 256;\n\tmov.b64 db, {lb, %3};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
+      "add.u32 ta, %1, 24;\n\tadd.u32 lb, %2, 384;\n\tmov.b64 db, {lb, %3};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
+      "add.u32 ta, %1, 32;\n\tadd.u32 lb, %2, 512;\n\tmov.b64 db, {lb, %3};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
+      "add.u32 ta, %1, 40;\n\tadd.u32 lb, %2, 640;\n\tmov.b64 db, {lb, %3};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
+      "add.u32 ta, %1, 48;\n\tadd.u32 lb, %2, 768;\n\tmov.b64 db, {lb, %3};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
+      "add.u32 ta, %1, 56;\n\tadd.u32 lb, %2, 896;\n\tmov.b64 db, {lb, %3};\n\t"
+      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(issue)
+      : "memory");
+}
 // Arrive once on `bar` when every tcgen05 operation the issuing lane started so far is done.
 __device__ __forceinline__ void mma_commit(uint32_t bar, uint32_t issue) {
   asm volatile(
