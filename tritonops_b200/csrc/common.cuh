@@ -27,7 +27,10 @@ int kv_append(const b200attn_kv_append_args* a, cudaStream_t stream);
 template <typename T>
 __device__ __forceinline__ uint4 ld_nc_16(const T* ptr) {
   uint4 r;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+#ifndef B200ATTN_LD_HINT
+#define B200ATTN_LD_HINT ".L2::256B"
+#endif
+  asm volatile("ld.global.nc.L1::no_allocate" B200ATTN_LD_HINT ".v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
                : "l"(ptr));
   return r;

@@ -159,9 +159,11 @@ __global__ void __launch_bounds__(kDecodeThreads, kDecodeCtasPerSm)
 decode_split_kernel(const DecodeParams p) {
   constexpr int KC = UnitRegs<D>::KC, DH = UnitRegs<D>::DH;
   constexpr int NMT = 4 * DH;  // 16-row d tiles of O^T
-  const int chunk_id = blockIdx.x;
-  const int hk = blockIdx.y / p.ggroups;
-  const int gg = blockIdx.y % p.ggroups;
+  // KV heads vary fastest in launch order: the CTAs resident together then read
+  // neighbouring 256-byte pieces of the same token rows (same DRAM pages)
+  const int hk = blockIdx.x / p.ggroups;
+  const int gg = blockIdx.x % p.ggroups;
+  const int chunk_id = blockIdx.y;
   const int b = blockIdx.z;
   const KeyMap km = make_keymap(p, b, hk);
   const int c_begin = chunk_id * p.chunk;
@@ -444,9 +446,9 @@ int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t
   long long rows = (long long)a->batch * a->heads_q * p.max_chunks;
   p.part_o = (float*)ws;
   p.part_lse = p.part_o + rows * a->head_dim;
-  if ((long long)a->heads_kv * p.ggroups > 65535) return B200ATTN_ERR_TOO_LARGE;
+  if (p.max_chunks > 65535) return B200ATTN_ERR_TOO_LARGE;
 
-  dim3 g1(p.max_chunks, a->heads_kv * p.ggroups, a->batch);
+  dim3 g1(a->heads_kv * p.ggroups, p.max_chunks, a->batch);
   dim3 g2(a->heads_q, a->batch);
   set_launch_count(2);
   return a->dtype == B200ATTN_F16 ? launch_decode_d<__half>(a->head_dim, p, g1, g2, stream)
