@@ -92,9 +92,14 @@ def test_decode_validation_codes(lib):
 
 def test_decode_workspace_formula(lib):
     from tritonops_b200._lib import DecodeArgs
-    a = DecodeArgs(batch=64, heads_q=32, heads_kv=8, head_dim=128, max_seqlen=8192)
+    a = DecodeArgs(batch=64, heads_q=32, heads_kv=8, head_dim=128, max_seqlen=8192, chunk_tokens=512)
     rows = 64 * 32 * 16
     assert lib.b200attn_decode_workspace_bytes(C.byref(a)) == rows * 128 * 4 + rows * 4
+    a.chunk_tokens = 0                        # automatic: 2048-key chunks for this size
+    assert lib.b200attn_decode_workspace_bytes(C.byref(a)) == 64 * 32 * 4 * (128 * 4 + 4)
+    a.batch = 1                               # few units: short chunks for parallelism
+    assert lib.b200attn_decode_workspace_bytes(C.byref(a)) == 1 * 32 * 64 * (128 * 4 + 4)
+    a.batch, a.chunk_tokens = 64, 512
     a.sparsity, a.window_global, a.window_local = 1, 64, 1024
     assert lib.b200attn_decode_workspace_bytes(C.byref(a)) == 64 * 32 * 3 * (128 * 4 + 4)
 

@@ -25,6 +25,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace b200attn {
 
@@ -47,6 +48,7 @@ struct DecodeParams {
   int batch, heads_q, heads_kv, group, ggroups;
   int chunk, max_chunks;
   int sparsity, win_global, win_local, block_size, max_sel;
+  int head_dim_rt;
   float scale_log2;
 };
 
@@ -315,6 +317,260 @@ decode_split_kernel(const DecodeParams p) {
   }
 }
 
+// --------------------------------------------------------------------------
+// TMA variant of phase 1.  Same work split (one CTA per sequence, KV-head
+// group and 512-key chunk) and the same partials, but K and V reach the SM as
+// bulk tensor copies: a producer warp streams 64-key stages (four 16-key boxes
+// per operand and 64-column panel, 128-byte swizzle) through a shared-memory
+// ring guarded by full / empty mbarriers, so the bytes in flight per SM are set
+// by the ring depth rather than by the load/store unit's outstanding requests,
+// and four consumer warps read their 16 keys of each stage with ldmatrix.
+// Up to 16 query heads of a GQA group ride in one MMA tile (M = 16).
+// --------------------------------------------------------------------------
+constexpr int kStageTok = 64;   // keys per ring stage
+constexpr int kBoxTok = 16;     // keys per TMA box (window / block gathers are 16-key aligned)
+
+template <int DP>
+struct DecodeTmaSmem {
+  static constexpr int kPanels = DP / 64;
+  static constexpr int kPanelBytes = kStageTok * 128;
+  static constexpr int kTileBytes = kPanels * kPanelBytes;   // K or V of one stage
+  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kStages = DP == 128 ? 3 : 5;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kBytes = kBarOffset + 2 * kStages * 8 + 16;
+  static constexpr int kAlloc = kBytes + 1024;
+  static constexpr int kCombinePitch = DP + 1;                // floats per (warp, head) row of the combine buffer
+  static_assert(4 * 16 * kCombinePitch * 4 + 2 * 4 * 16 * 4 <= kStages * kStageBytes, "combine buffer aliases the ring");
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+template <typename T, int DP>
+__global__ void __launch_bounds__(160, 2)
+decode_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                        const DecodeParams p) {
+  using L = DecodeTmaSmem<DP>;
+  using namespace sm100;
+  constexpr int NKT = DP / 16;   // 16-wide d steps of the score product
+  constexpr int NDT = DP / 8;    // 8-wide d tiles of the output
+  const int hk = blockIdx.x / p.ggroups;
+  const int gg = blockIdx.x % p.ggroups;   // group of 16 query heads inside the GQA group
+  const int chunk_id = blockIdx.y;
+  const int b = blockIdx.z;
+  const KeyMap km = make_keymap(p, b, hk);
+  const int c_begin = chunk_id * p.chunk;
+  if (c_begin >= km.n) return;
+  const int c_end = min(km.n, c_begin + p.chunk);
+  const int n_tiles = (c_end - c_begin + kStageTok - 1) / kStageTok;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  const uint32_t bars = sbase + L::kBarOffset;
+  auto full = [&](int s) { return bars + 8 * s; };
+  auto empty = [&](int s) { return bars + 8 * (L::kStages + s); };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kBarOffset + 2 * L::kStages * 8);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < L::kStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 4); }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+
+  if (warp == 4) {
+    // ================================================================ producer
+    if (lane == 0) {
+      prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+      for (int tile = 0; tile < n_tiles; ++tile) {
+        const int s = tile % L::kStages;
+        mbar_wait(empty(s), ((tile / L::kStages) & 1) ^ 1, abort_flag);
+        const int v0 = c_begin + tile * kStageTok;
+        const int nbox = min(kStageTok / kBoxTok, (c_end - v0 + kBoxTok - 1) / kBoxTok);
+        mbar_expect_tx(full(s), nbox * 2 * L::kPanels * kBoxTok * 128);
+        const uint32_t kdst = sbase + s * L::kStageBytes, vdst = kdst + L::kTileBytes;
+        for (int i = 0; i < nbox; ++i) {
+          const int tok = km.to_token(v0 + kBoxTok * i);   // 16 consecutive cache rows (rows past the end are masked)
+          for (int pn = 0; pn < L::kPanels; ++pn) {
+            const uint32_t off = pn * L::kPanelBytes + i * kBoxTok * 128;
+            tma_load_4d(kdst + off, &tmap_k, full(s), 64 * pn, tok, hk, b);
+            tma_load_4d(vdst + off, &tmap_v, full(s), 64 * pn, tok, hk, b);
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // ================================================================== consumers
+  const int gid = lane >> 2, tig = lane & 3;
+  const int g0 = gg * 16 + gid, g1 = g0 + 8;          // query heads of this lane's two MMA rows
+  const T* qbase = (const T*)p.q + (long long)b * p.q_sb + (long long)(hk * p.group) * p.q_sh;
+  unsigned qa[NKT][4];
+#pragma unroll
+  for (int kt = 0; kt < NKT; ++kt) {
+    const int d = 16 * kt + 2 * tig;
+    const bool dok0 = d < p.head_dim_rt, dok1 = d + 8 < p.head_dim_rt;
+    qa[kt][0] = (g0 < p.group && dok0) ? *reinterpret_cast<const unsigned*>(qbase + (long long)g0 * p.q_sh + d) : 0u;
+    qa[kt][1] = (g1 < p.group && dok0) ? *reinterpret_cast<const unsigned*>(qbase + (long long)g1 * p.q_sh + d) : 0u;
+    qa[kt][2] = (g0 < p.group && dok1) ? *reinterpret_cast<const unsigned*>(qbase + (long long)g0 * p.q_sh + d + 8) : 0u;
+    qa[kt][3] = (g1 < p.group && dok1) ? *reinterpret_cast<const unsigned*>(qbase + (long long)g1 * p.q_sh + d + 8) : 0u;
+  }
+  float acc[NDT][4];
+#pragma unroll
+  for (int i = 0; i < NDT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int s = tile % L::kStages;
+    mbar_wait(full(s), (tile / L::kStages) & 1, abort_flag);
+    const int v0 = c_begin + tile * kStageTok + 16 * warp;   // this warp's 16 keys of the stage
+    if (v0 < c_end) {
+      const uint32_t ktile = sbase + s * L::kStageBytes, vtile = ktile + L::kTileBytes;
+      // which of the 16 keys are real (inside the chunk and inside the sequence)
+      bool ok = false;
+      if (lane < 16) {
+        const int vp = v0 + lane;
+        if (vp < c_end) {
+          const int tok = km.to_token(v0 & ~(kBoxTok - 1)) + (lane & (kBoxTok - 1));
+          ok = tok >= 0 && tok < km.len;
+        }
+      }
+      const unsigned vmask = __ballot_sync(0xffffffffu, ok) & 0xffffu;
+      if (vmask != 0xffffu) {
+        // rows of V that are not real keys may hold anything (cache padding): P = 0
+        // times NaN would poison O, so they are cleared in shared memory first
+        uint8_t* vgen = sgen + (vtile - sbase);
+        for (int r = 0; r < 16; ++r) {
+          if ((vmask >> r) & 1u) continue;
+          const int row = 16 * warp + r;
+          for (int i = lane; i < L::kPanels * 8; i += 32)
+            *reinterpret_cast<uint4*>(vgen + (i >> 3) * L::kPanelBytes + row * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async();   // these plain stores precede the copy engine's next write to the stage
+        __syncwarp();
+      }
+      // ---- S[g, key] = Q K^T for two 8-key tiles
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        const int mi = lane >> 3, r = lane & 7;
+        const int row = 16 * warp + 8 * (mi >> 1) + r;
+#pragma unroll
+        for (int kt = 0; kt < NKT; ++kt) {
+          const int c16 = 2 * kt + (mi & 1);
+          const uint32_t addr = ktile + (c16 >> 3) * L::kPanelBytes + row * 128 + (((c16 & 7) ^ (row & 7)) << 4);
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4(addr, b0, b1, b2, b3);
+          mma_16816<T>(c0, qa[kt][0], qa[kt][1], qa[kt][2], qa[kt][3], b0, b1);
+          mma_16816<T>(c1, qa[kt][0], qa[kt][1], qa[kt][2], qa[kt][3], b2, b3);
+        }
+      }
+      // columns of this thread: keys 2tig, 2tig+1 (c0) and 8+2tig, 9+2tig (c1); rows gid (x0,x1) and gid+8 (x2,x3)
+      float sc[2][4];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        sc[r][0] = ((vmask >> (2 * tig)) & 1u) ? c0[2 * r] * p.scale_log2 : -INFINITY;
+        sc[r][1] = ((vmask >> (2 * tig + 1)) & 1u) ? c0[2 * r + 1] * p.scale_log2 : -INFINITY;
+        sc[r][2] = ((vmask >> (8 + 2 * tig)) & 1u) ? c1[2 * r] * p.scale_log2 : -INFINITY;
+        sc[r][3] = ((vmask >> (9 + 2 * tig)) & 1u) ? c1[2 * r + 1] * p.scale_log2 : -INFINITY;
+      }
+      float alpha[2];
+      unsigned pa[4];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float mx = fmaxf(fmaxf(sc[r][0], sc[r][1]), fmaxf(sc[r][2], sc[r][3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[r], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[r] = exp2f(m_run[r] - m_use);
+        m_run[r] = m_new;
+        const float p0 = exp2f(sc[r][0] - m_use), p1 = exp2f(sc[r][1] - m_use);
+        const float p2 = exp2f(sc[r][2] - m_use), p3 = exp2f(sc[r][3] - m_use);
+        l_run[r] = l_run[r] * alpha[r] + ((p0 + p1) + (p2 + p3));
+        pa[r] = pack2<T>(p0, p1);        // A fragment: row gid (+8), keys 2tig, 2tig+1
+        pa[2 + r] = pack2<T>(p2, p3);    //             row gid (+8), keys 8+2tig, 9+2tig
+      }
+      if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+        for (int i = 0; i < NDT; ++i) {
+          acc[i][0] *= alpha[0]; acc[i][1] *= alpha[0];
+          acc[i][2] *= alpha[1]; acc[i][3] *= alpha[1];
+        }
+      }
+      // ---- O[g, d] += P V
+      {
+        const int mi = lane >> 3, r = lane & 7;
+        const int row = 16 * warp + 8 * (mi & 1) + r;
+#pragma unroll
+        for (int dp = 0; dp < NDT / 2; ++dp) {
+          const int c16 = 2 * dp + (mi >> 1);
+          const uint32_t addr = vtile + (c16 >> 3) * L::kPanelBytes + row * 128 + (((c16 & 7) ^ (row & 7)) << 4);
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+          mma_16816<T>(acc[2 * dp], pa[0], pa[1], pa[2], pa[3], b0, b1);
+          mma_16816<T>(acc[2 * dp + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty(s));
+  }
+
+  // ---- combine the four warps (the ring is free now: every stage was consumed)
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  float* sm_o = reinterpret_cast<float*>(sgen);                       // [4][16][DP + 1]
+  float* sm_m = sm_o + 4 * 16 * L::kCombinePitch;                      // [4][16]
+  float* sm_l = sm_m + 4 * 16;
+  if (tig == 0) {
+    sm_m[warp * 16 + gid] = m_run[0]; sm_m[warp * 16 + gid + 8] = m_run[1];
+    sm_l[warp * 16 + gid] = l_run[0]; sm_l[warp * 16 + gid + 8] = l_run[1];
+  }
+#pragma unroll
+  for (int i = 0; i < NDT; ++i) {
+    float* r0 = sm_o + (warp * 16 + gid) * L::kCombinePitch + 8 * i + 2 * tig;
+    float* r1 = sm_o + (warp * 16 + gid + 8) * L::kCombinePitch + 8 * i + 2 * tig;
+    r0[0] = acc[i][0]; r0[1] = acc[i][1];
+    r1[0] = acc[i][2]; r1[1] = acc[i][3];
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  const int heads_here = min(16, p.group - gg * 16);
+  const int D = p.head_dim_rt;
+  for (int idx = threadIdx.x; idx < heads_here * D; idx += 128) {
+    const int g = idx / D, d = idx - g * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + g]);
+    const float Ms = (M == -INFINITY) ? 0.f : M;
+    float Lsum = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(sm_m[w * 16 + g] - Ms);
+      Lsum += sm_l[w * 16 + g] * f;
+      O += sm_o[(w * 16 + g) * L::kCombinePitch + d] * f;
+    }
+    const int hq = hk * p.group + gg * 16 + g;
+    const long long row = ((long long)b * p.heads_q + hq) * p.max_chunks + chunk_id;
+    p.part_o[row * D + d] = Lsum > 0.f ? O / Lsum : 0.f;
+    if (d == 0) p.part_lse[row] = Lsum > 0.f ? Ms + log2f(Lsum) : -INFINITY;
+  }
+}
+
 // Phase 2: O = sum_c o_c * 2^(lse_c - lse), lse = log2 sum_c 2^lse_c
 // (flash_attn_decoding.py:173-208).  Sequences without visible keys give 0.
 template <typename T, int D>
@@ -350,8 +606,19 @@ static int decode_max_visible(const b200attn_decode_args* a) {
   return a->max_seqlen;
 }
 
+// Split size.  Longer chunks amortise a CTA's pipeline fill and combine (config 3:
+// 5.5 TB/s at 512 keys, 6.35 TB/s at 2048) but give fewer CTAs; without a request
+// from the caller take the longest chunk that still yields about four CTAs per
+// resident slot (2 per SM) when every sequence has max_seqlen keys.
 static int decode_chunk(const b200attn_decode_args* a) {
-  return a->chunk_tokens > 0 ? a->chunk_tokens : 512;
+  if (a->chunk_tokens > 0) return a->chunk_tokens;
+  const long long group = a->heads_kv > 0 ? a->heads_q / a->heads_kv : 1;
+  const long long units = (long long)a->batch * a->heads_kv * ((group + 15) / 16);
+  const long long visible = decode_max_visible(a);
+  const int sizes[5] = {2048, 1024, 512, 256, 128};
+  for (int c : sizes)
+    if (units * ((visible + c - 1) / c) >= 4 * 2 * 148) return c;
+  return 128;
 }
 
 size_t decode_workspace_bytes(const b200attn_decode_args* a) {
@@ -412,6 +679,73 @@ static int launch_decode_d(int D, const DecodeParams& p, dim3 g1, dim3 g2, cudaS
   }
 }
 
+
+// ---- host side of the TMA variant
+typedef CUresult (*DecEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static DecEncodeFn dec_encode_fn() {
+  static DecEncodeFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return (DecEncodeFn)f;
+  }();
+  return fn;
+}
+// [D, keys, kv heads, batch] view of a cache, box = 64 x 16 x 1 x 1, 128-byte swizzle
+static bool make_cache_tmap(CUtensorMap* m, int dtype, const void* base, int D, long long keys, int heads, int batch,
+                            long long st, long long sh, long long sb) {
+  DecEncodeFn enc = dec_encode_fn();
+  if (!enc) return false;
+  if (batch <= 1 || sb <= 0) sb = st * keys;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)keys, (cuuint64_t)heads, (cuuint64_t)batch};
+  cuuint64_t strides[3] = {(cuuint64_t)st * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)kBoxTok, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(m, dtype == B200ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int DP>
+static int launch_decode_tma_d(const b200attn_decode_args* a, const DecodeParams& p, dim3 g1, dim3 g2,
+                               cudaStream_t stream) {
+  using L = DecodeTmaSmem<DP>;
+  CUtensorMap tk, tv;
+  // keys beyond max_seqlen are never visible; the copy engine zero-fills past that extent
+  if (!make_cache_tmap(&tk, a->dtype, a->k_cache, a->head_dim, a->max_seqlen, a->heads_kv, a->batch,
+                       a->k_stride_t, a->k_stride_h, a->k_stride_b) ||
+      !make_cache_tmap(&tv, a->dtype, a->v_cache, a->head_dim, a->max_seqlen, a->heads_kv, a->batch,
+                       a->v_stride_t, a->v_stride_h, a->v_stride_b))
+    return B200ATTN_ERR_CUDA;
+  auto kern = decode_split_tma_kernel<T, DP>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
+      return B200ATTN_ERR_CUDA;
+    attr_set = true;
+  }
+  kern<<<g1, 160, L::kAlloc, stream>>>(tk, tv, p);
+  switch (a->head_dim) {
+    case 32: decode_combine_kernel<T, 32><<<g2, 128, 0, stream>>>(p); break;
+    case 64: decode_combine_kernel<T, 64><<<g2, 128, 0, stream>>>(p); break;
+    case 96: decode_combine_kernel<T, 96><<<g2, 128, 0, stream>>>(p); break;
+    default: decode_combine_kernel<T, 128><<<g2, 128, 0, stream>>>(p); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+}
+
+template <typename T>
+static int launch_decode_tma(const b200attn_decode_args* a, const DecodeParams& p, dim3 g1, dim3 g2,
+                             cudaStream_t stream) {
+  return a->head_dim <= 64 ? launch_decode_tma_d<T, 64>(a, p, g1, g2, stream)
+                           : launch_decode_tma_d<T, 128>(a, p, g1, g2, stream);
+}
+
 // scratch == nullptr: use the caller's workspace from the args.
 int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t scratch_bytes,
                cudaStream_t stream) {
@@ -443,14 +777,24 @@ int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t
   p.win_global = a->window_global; p.win_local = a->window_local;
   p.block_size = a->block_size; p.max_sel = a->max_sel;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  p.head_dim_rt = a->head_dim;
   long long rows = (long long)a->batch * a->heads_q * p.max_chunks;
   p.part_o = (float*)ws;
   p.part_lse = p.part_o + rows * a->head_dim;
   if (p.max_chunks > 65535) return B200ATTN_ERR_TOO_LARGE;
 
-  dim3 g1(a->heads_kv * p.ggroups, p.max_chunks, a->batch);
   dim3 g2(a->heads_q, a->batch);
   set_launch_count(2);
+  // bulk-copy path unless a window edge is not 16-key aligned (a box must not straddle it)
+  const bool tma_ok = !(eff.sparsity == B200ATTN_WINDOW && (a->window_global % kBoxTok) != 0) &&
+                      a->max_seqlen > 0;
+  if (tma_ok) {
+    p.ggroups = (p.group + 15) / 16;
+    dim3 g1t(a->heads_kv * p.ggroups, p.max_chunks, a->batch);
+    return a->dtype == B200ATTN_F16 ? launch_decode_tma<__half>(a, p, g1t, g2, stream)
+                                    : launch_decode_tma<__nv_bfloat16>(a, p, g1t, g2, stream);
+  }
+  dim3 g1(a->heads_kv * p.ggroups, p.max_chunks, a->batch);
   return a->dtype == B200ATTN_F16 ? launch_decode_d<__half>(a->head_dim, p, g1, g2, stream)
                                   : launch_decode_d<__nv_bfloat16>(a->head_dim, p, g1, g2, stream);
 }
