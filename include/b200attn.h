@@ -181,6 +181,110 @@ int b200attn_sparse_decode_fwd(const b200attn_decode_args* args, b200attn_stream
 int b200attn_decode_fwd_noalloc(const b200attn_decode_args* args, b200attn_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * Decoding over a paged KV cache.
+ *
+ * k_pages / v_pages are pools [num_pages, page_size, heads_kv, head_dim];
+ * page_table[b][i] is the pool page that holds keys i*page_size .. of sequence
+ * b (entries at or beyond ceil(len_b / page_size) are not read).  Pages must
+ * follow one another in memory: *_stride_page == page_size * *_stride_t.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const void* q;               /* [batch, heads_q, head_dim] */
+  const void* k_pages;
+  const void* v_pages;
+  void* o;                     /* like q */
+  int32_t dtype;
+  int32_t batch, heads_q, heads_kv, head_dim;
+  int32_t page_size;           /* keys per page, a multiple of 16 */
+  int32_t num_pages;           /* pages in the pool */
+  int32_t max_pages_per_seq;   /* row length of page_table */
+  int32_t max_seqlen;          /* upper bound on the lengths */
+  const int32_t* page_table;   /* int32 [batch, max_pages_per_seq] */
+  const int32_t* seqlens;      /* int32 [batch] */
+  int64_t q_stride_b, q_stride_h;
+  int64_t k_stride_page, k_stride_t, k_stride_h;
+  int64_t v_stride_page, v_stride_t, v_stride_h;
+  int64_t o_stride_b, o_stride_h;
+  float softmax_scale;         /* natural scale */
+  int32_t chunk_tokens;        /* as in b200attn_decode_args */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status_word;        /* nullable, reserved */
+} b200attn_paged_decode_args;
+
+size_t b200attn_paged_decode_workspace_bytes(const b200attn_paged_decode_args* args);
+
+/* GQA split-KV decoding whose keys are found through a page table; same
+ * arithmetic as b200attn_decode_fwd on the equivalent padded cache.  The
+ * reference has no paged form: its decoding kernels index one padded cache
+ * per sequence (flash_attn_triton/flash_attn_decoding.py:62-69); here the row
+ * of key t is looked up per page instead of being b * stride + t. */
+int b200attn_paged_decode_fwd(const b200attn_paged_decode_args* args, b200attn_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Block selection: building the block lists the BLOCK_LIST modes take, on the
+ * device, with no host work between the producer of the pattern and the
+ * attention launch.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  int32_t* block_idx;          /* out int32 [batch, heads, n_qblocks, max_nnz], ascending, -1 padded */
+  int32_t* block_cnt;          /* out int32 [batch, heads, n_qblocks] */
+  int32_t batch, heads, n_qblocks, max_nnz;
+  int32_t block_size;
+  int32_t window_local, window_global;
+} b200attn_window_blocks_prefill_args;
+
+/* Upper bound on the blocks one query block can select (sizes max_nnz). */
+int32_t b200attn_window_blocks_prefill_max_nnz(int32_t block_size, int32_t window_local, int32_t window_global,
+                                               int32_t n_qblocks);
+
+/* The block cover of the reference's window pattern for prefill: query block i
+ * lists KV block j <= i iff some query of block i sees some key of block j
+ * under "i_q - j_k < window_local or j_k < window_global"
+ * (flash_attn_triton/flash_attn_sparse_attn_triton.py:125-129, 178-183 give
+ * the same two key ranges per query tile).  Whole listed blocks are attended,
+ * so the result is a superset of the exact window; B200ATTN_ERR_TOO_LARGE if a
+ * row needs more than max_nnz entries. */
+int b200attn_window_blocks_prefill(const b200attn_window_blocks_prefill_args* args, b200attn_stream_t stream);
+
+typedef struct {
+  int32_t* block_idx;          /* out int32 [batch, heads_kv, max_sel], ascending, -1 padded */
+  int32_t* block_cnt;          /* out int32 [batch, heads_kv] */
+  const int32_t* cu_seqlens;   /* nullable; give one of the two, as for decoding */
+  const int32_t* seqlens;
+  int32_t batch, heads_kv, max_sel;
+  int32_t block_size;
+  int32_t window_local, window_global;
+} b200attn_window_blocks_decode_args;
+
+/* The blocks that hold keys "j < window_global or j >= len - window_local" of
+ * each sequence (flash_attn_triton/flash_attn_decoding_sparse.py:52-58, 82-85;
+ * the wrapper's chunk count :256-266 is the same cover in units of
+ * window_global).  Rows that would need more than max_sel entries keep the
+ * first max_sel. */
+int b200attn_window_blocks_decode(const b200attn_window_blocks_decode_args* args, b200attn_stream_t stream);
+
+typedef struct {
+  const float* scores;         /* fp32 [rows, n_blocks] block scores, larger = more important */
+  int64_t score_stride_row;    /* elements between rows */
+  const int32_t* n_valid;      /* nullable int32 [rows]: only blocks 0 .. n_valid-1 are candidates
+                                  (causal prefill: query block + 1; decoding: ceil(len / block)) */
+  int32_t rows, n_blocks;      /* n_blocks <= 8192 */
+  int32_t top_k;               /* entries per output row */
+  int32_t force_first;         /* this many leading candidate blocks are always taken (attention sinks) */
+  int32_t force_last;          /* this many trailing candidate blocks are always taken (the diagonal / newest block) */
+  int32_t* block_idx;          /* out int32 [rows, top_k], ascending, -1 padded */
+  int32_t* block_cnt;          /* out int32 [rows] = min(top_k, candidates) */
+} b200attn_topk_blocks_args;
+
+/* Per row, the top_k highest-scoring candidate blocks, returned in ascending
+ * block order as the BLOCK_LIST modes want them.  Ties go to the lower block
+ * number and NaN scores rank last, so the result is a pure function of the
+ * scores.  No counterpart in the reference, whose sparsity is fixed to the
+ * window pattern (flash_attn_triton/flash_attn_decoding_sparse.py:82-85). */
+int b200attn_topk_blocks(const b200attn_topk_blocks_args* args, b200attn_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * Dense prefill backward.  Tensors and addressing forms as in
  * b200attn_prefill_args; o and lse are the forward's outputs, d_o the
  * gradient of o; dq like q, dk / dv like k / v (the query heads of a GQA group

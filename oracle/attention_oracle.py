@@ -443,3 +443,67 @@ def window_to_block_lists(n: int, block: int, local: int, glob: int):
         idx[i, :len(r)] = torch.tensor(r, dtype=torch.int32)
         cnt[i] = len(r)
     return idx, cnt
+
+
+def window_decode_block_cover(lens: Sequence[int], block: int, local: int, glob: int, max_sel: int):
+    """Blocks holding at least one visible key of the decoding window pattern
+    (flash_attn_decoding_sparse.py:82-85), per sequence, ascending, first
+    max_sel kept: (idx [B, max_sel] padded with -1, cnt [B])."""
+    vis = window_decode_visible(local, glob)
+    idx = torch.full((len(lens), max_sel), -1, dtype=torch.int32)
+    cnt = torch.zeros(len(lens), dtype=torch.int32)
+    for b, n in enumerate(lens):
+        n = max(int(n), 0)
+        m = vis(b, n)
+        act = [kb for kb in range((n + block - 1) // block) if bool(m[kb * block:(kb + 1) * block].any())]
+        act = act[:max_sel]
+        idx[b, :len(act)] = torch.tensor(act, dtype=torch.int32)
+        cnt[b] = len(act)
+    return idx, cnt
+
+
+def topk_blocks(scores, top_k: int, n_valid=None, force_first: int = 0, force_last: int = 0):
+    """Row-wise top-k block choice in ascending block order.  Candidates are
+    blocks 0..n_valid-1; the first force_first and last force_last candidates
+    always win; otherwise larger score wins, ties go to the lower block, NaN
+    ranks below -inf.  Returns (idx [rows, top_k] padded with -1, cnt [rows])."""
+    import numpy as np
+    s = np.asarray(scores, dtype=np.float32)
+    rows, n = s.shape
+    idx = np.full((rows, top_k), -1, dtype=np.int32)
+    cnt = np.zeros(rows, dtype=np.int32)
+    for r in range(rows):
+        nv = n if n_valid is None else max(0, min(int(n_valid[r]), n))
+        # rank key: (class, score); class 2 forced, 1 real number, 0 NaN
+        order = []
+        for j in range(nv):
+            forced = j < force_first or j >= nv - force_last
+            x = float(s[r, j])
+            if forced:
+                key = (2, 0.0)
+            elif x != x:
+                key = (0, 0.0)
+            else:
+                key = (1, x)
+            order.append((key, j))
+        order.sort(key=lambda t: (-t[0][0], -t[0][1], t[1]))
+        take = sorted(j for _, j in order[:min(top_k, nv)])
+        idx[r, :len(take)] = take
+        cnt[r] = len(take)
+    return torch.from_numpy(idx), torch.from_numpy(cnt)
+
+
+def paged_to_padded(pages, page_table, seqlens, capacity=None):
+    """Gather a page pool [P, page, H, D] into the padded cache [B, capacity, H, D]
+    the reference's decoding kernels index (flash_attn_decoding.py:62-69)."""
+    P, page, H, D = pages.shape
+    B = page_table.shape[0]
+    cap = capacity or page_table.shape[1] * page
+    out = torch.zeros(B, cap, H, D, dtype=pages.dtype)
+    for b in range(B):
+        n = max(int(seqlens[b]), 0)
+        for i in range((n + page - 1) // page):
+            t0 = i * page
+            t1 = min(n, t0 + page)
+            out[b, t0:t1] = pages[int(page_table[b, i]), :t1 - t0]
+    return out

@@ -165,3 +165,49 @@ def test_prefill_bwd_validation_codes(lib):
     assert lib.b200attn_prefill_bwd_workspace_bytes(C.byref(a)) == rows * 64 * 4 + rows * 4
     a.dk_stride_t = 4
     assert lib.b200attn_prefill_bwd(C.byref(a), None) == -6
+
+
+def test_struct_sizes_of_selection_and_paged_args(lib):
+    import subprocess
+    import tempfile
+    from tritonops_b200 import _lib
+    names = [("b200attn_paged_decode_args", _lib.PagedDecodeArgs),
+             ("b200attn_window_blocks_prefill_args", _lib.WindowBlocksPrefillArgs),
+             ("b200attn_window_blocks_decode_args", _lib.WindowBlocksDecodeArgs),
+             ("b200attn_topk_blocks_args", _lib.TopkBlocksArgs),
+             ("b200attn_kv_pack_args", _lib.KvPackArgs), ("b200attn_kv_append_args", _lib.KvAppendArgs)]
+    with tempfile.TemporaryDirectory() as d:
+        src = os.path.join(d, "p.c")
+        body = "".join(f'printf("%zu\\n", sizeof({n}));' for n, _ in names)
+        open(src, "w").write('#include <stdio.h>\n#include "b200attn.h"\nint main(){' + body + 'return 0;}\n')
+        exe = os.path.join(d, "p")
+        subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), src, "-o", exe])
+        sizes = list(map(int, subprocess.check_output([exe]).split()))
+    for (n, cls), size in zip(names, sizes):
+        assert size == C.sizeof(cls), n
+    assert _lib.PagedDecodeArgs.workspace_bytes.offset % 8 == 0
+
+
+def test_window_cover_width_is_host_side_and_matches_brute_force(lib):
+    """b200attn_window_blocks_prefill_max_nnz needs no GPU; it must equal the widest
+    row of the brute-force block cover of the window mask."""
+    from oracle import attention_oracle as orc
+    L = lib
+    for nqb in (1, 3, 12):
+        for local, glob in [(64, 64), (200, 256), (1, 0), (0, 128), (2, 0), (65, 1), (0, 0), (129, 100)]:
+            _, cnt = orc.window_to_block_lists(nqb * 64, 64, local, glob)
+            assert L.b200attn_window_blocks_prefill_max_nnz(64, local, glob, nqb) == int(cnt.max())
+
+
+def test_new_entry_points_validate_before_touching_the_device(lib):
+    from tritonops_b200 import _lib
+    L = lib
+    a = _lib.TopkBlocksArgs()
+    assert L.b200attn_topk_blocks(C.byref(a), None) == -1
+    b = _lib.WindowBlocksPrefillArgs()
+    assert L.b200attn_window_blocks_prefill(C.byref(b), None) == -1
+    c = _lib.WindowBlocksDecodeArgs()
+    assert L.b200attn_window_blocks_decode(C.byref(c), None) == -1
+    d = _lib.PagedDecodeArgs()
+    assert L.b200attn_paged_decode_fwd(C.byref(d), None) == -1
+    assert L.b200attn_paged_decode_workspace_bytes(C.byref(d)) == 0

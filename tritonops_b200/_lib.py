@@ -75,6 +75,40 @@ class KvAppendArgs(C.Structure):
                 ("cache_stride_b", i64), ("cache_stride_t", i64), ("cache_stride_h", i64)]
 
 
+class PagedDecodeArgs(C.Structure):
+    _fields_ = [
+        ("q", vp), ("k_pages", vp), ("v_pages", vp), ("o", vp),
+        ("dtype", i32), ("batch", i32), ("heads_q", i32), ("heads_kv", i32), ("head_dim", i32),
+        ("page_size", i32), ("num_pages", i32), ("max_pages_per_seq", i32), ("max_seqlen", i32),
+        ("page_table", vp), ("seqlens", vp),
+        ("q_stride_b", i64), ("q_stride_h", i64),
+        ("k_stride_page", i64), ("k_stride_t", i64), ("k_stride_h", i64),
+        ("v_stride_page", i64), ("v_stride_t", i64), ("v_stride_h", i64),
+        ("o_stride_b", i64), ("o_stride_h", i64),
+        ("softmax_scale", f32), ("chunk_tokens", i32),
+        ("workspace", vp), ("workspace_bytes", C.c_size_t), ("status_word", vp),
+    ]
+
+
+class WindowBlocksPrefillArgs(C.Structure):
+    _fields_ = [("block_idx", vp), ("block_cnt", vp),
+                ("batch", i32), ("heads", i32), ("n_qblocks", i32), ("max_nnz", i32),
+                ("block_size", i32), ("window_local", i32), ("window_global", i32)]
+
+
+class WindowBlocksDecodeArgs(C.Structure):
+    _fields_ = [("block_idx", vp), ("block_cnt", vp), ("cu_seqlens", vp), ("seqlens", vp),
+                ("batch", i32), ("heads_kv", i32), ("max_sel", i32),
+                ("block_size", i32), ("window_local", i32), ("window_global", i32)]
+
+
+class TopkBlocksArgs(C.Structure):
+    _fields_ = [("scores", vp), ("score_stride_row", i64), ("n_valid", vp),
+                ("rows", i32), ("n_blocks", i32), ("top_k", i32),
+                ("force_first", i32), ("force_last", i32),
+                ("block_idx", vp), ("block_cnt", vp)]
+
+
 # every symbol include/b200attn.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "b200attn_abi_version": (C.c_int, []),
@@ -91,6 +125,12 @@ SYMBOLS = {
     "b200attn_prefill_bwd": (C.c_int, [C.POINTER(PrefillBwdArgs), vp]),
     "b200attn_kv_pack_to_cache": (C.c_int, [C.POINTER(KvPackArgs), vp]),
     "b200attn_kv_append": (C.c_int, [C.POINTER(KvAppendArgs), vp]),
+    "b200attn_paged_decode_workspace_bytes": (C.c_size_t, [C.POINTER(PagedDecodeArgs)]),
+    "b200attn_paged_decode_fwd": (C.c_int, [C.POINTER(PagedDecodeArgs), vp]),
+    "b200attn_window_blocks_prefill_max_nnz": (i32, [i32, i32, i32, i32]),
+    "b200attn_window_blocks_prefill": (C.c_int, [C.POINTER(WindowBlocksPrefillArgs), vp]),
+    "b200attn_window_blocks_decode": (C.c_int, [C.POINTER(WindowBlocksDecodeArgs), vp]),
+    "b200attn_topk_blocks": (C.c_int, [C.POINTER(TopkBlocksArgs), vp]),
 }
 NOALLOC_SCRATCH_BYTES = 32 << 20
 

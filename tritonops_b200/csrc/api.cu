@@ -72,6 +72,35 @@ int b200attn_kv_append(const b200attn_kv_append_args* args, b200attn_stream_t st
   return kv_append(args, (cudaStream_t)stream);
 }
 
+size_t b200attn_paged_decode_workspace_bytes(const b200attn_paged_decode_args* args) {
+  return paged_decode_workspace_bytes(args);
+}
+
+int b200attn_paged_decode_fwd(const b200attn_paged_decode_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return paged_decode_fwd(args, (cudaStream_t)stream);
+}
+
+int32_t b200attn_window_blocks_prefill_max_nnz(int32_t block_size, int32_t window_local, int32_t window_global,
+                                               int32_t n_qblocks) {
+  return window_blocks_prefill_max_nnz(block_size, window_local, window_global, n_qblocks);
+}
+
+int b200attn_window_blocks_prefill(const b200attn_window_blocks_prefill_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return window_blocks_prefill(args, (cudaStream_t)stream);
+}
+
+int b200attn_window_blocks_decode(const b200attn_window_blocks_decode_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return window_blocks_decode(args, (cudaStream_t)stream);
+}
+
+int b200attn_topk_blocks(const b200attn_topk_blocks_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return topk_blocks(args, (cudaStream_t)stream);
+}
+
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args*) { return 0; }
 
 int b200attn_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream) {

@@ -22,6 +22,13 @@ size_t prefill_bwd_workspace_bytes(const b200attn_prefill_bwd_args* a);
 int prefill_bwd(const b200attn_prefill_bwd_args* a, cudaStream_t stream);
 int kv_pack_to_cache(const b200attn_kv_pack_args* a, cudaStream_t stream);
 int kv_append(const b200attn_kv_append_args* a, cudaStream_t stream);
+size_t paged_decode_workspace_bytes(const b200attn_paged_decode_args* a);
+int paged_decode_fwd(const b200attn_paged_decode_args* a, cudaStream_t stream);
+int32_t window_blocks_prefill_max_nnz(int32_t block_size, int32_t window_local, int32_t window_global,
+                                      int32_t n_qblocks);
+int window_blocks_prefill(const b200attn_window_blocks_prefill_args* a, cudaStream_t stream);
+int window_blocks_decode(const b200attn_window_blocks_decode_args* a, cudaStream_t stream);
+int topk_blocks(const b200attn_topk_blocks_args* a, cudaStream_t stream);
 
 // 16-byte read-only load that does not pollute L1 (data is used once).
 template <typename T>

@@ -32,6 +32,7 @@ namespace b200attn {
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kUnit = 16;  // tokens one warp handles per step
+constexpr int kPaged = 3;  // internal key map: every key of the sequence, found through a page table
 
 struct DecodeParams {
   const void* q;
@@ -50,6 +51,8 @@ struct DecodeParams {
   int sparsity, win_global, win_local, block_size, max_sel;
   int head_dim_rt;
   float scale_log2;
+  long long map_keys;  // host only: key extent and batch extent of the cache's tensor maps
+  int map_batch;
 };
 
 // How many keys sequence b / kv head hk attends to, and where they live.
@@ -58,7 +61,7 @@ struct DecodeParams {
 struct KeyMap {
   int n;       // number of visible keys
   int len;     // sequence length
-  int mode;
+  int mode;    // b200attn_sparsity, or kPaged
   int split;   // WINDOW: virtual positions >= split are shifted by `shift`
   int shift;
   int bshift;  // BLOCK_LIST: log2(block_size) when a power of two, else -1
@@ -90,6 +93,11 @@ __device__ __forceinline__ KeyMap make_keymap(const DecodeParams& p, int b, int 
     m.split = g;
     m.shift = start2 - g;
     m.n = g + (m.len - start2);
+  } else if (p.sparsity == kPaged) {
+    // key t lives in row page_table[b][t / page] * page + t % page of the pool
+    m.bsize = p.block_size;
+    m.blocks = p.block_idx + (long long)b * p.max_sel;
+    m.n = min(m.len, p.max_sel * p.block_size);
   } else {
     m.bsize = p.block_size;
     m.blocks = p.block_idx + ((long long)b * p.heads_kv + hk) * p.max_sel;
@@ -369,6 +377,7 @@ decode_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
   const int c_begin = chunk_id * p.chunk;
   if (c_begin >= km.n) return;
   const int c_end = min(km.n, c_begin + p.chunk);
+  const int map_b = km.mode == kPaged ? 0 : b;   // a page pool has no batch axis
   const int n_tiles = (c_end - c_begin + kStageTok - 1) / kStageTok;
 
   extern __shared__ uint8_t smem_raw[];
@@ -402,8 +411,8 @@ decode_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
           const int tok = km.to_token(v0 + kBoxTok * i);   // 16 consecutive cache rows (rows past the end are masked)
           for (int pn = 0; pn < L::kPanels; ++pn) {
             const uint32_t off = pn * L::kPanelBytes + i * kBoxTok * 128;
-            tma_load_4d(kdst + off, &tmap_k, full(s), 64 * pn, tok, hk, b);
-            tma_load_4d(vdst + off, &tmap_v, full(s), 64 * pn, tok, hk, b);
+            tma_load_4d(kdst + off, &tmap_k, full(s), 64 * pn, tok, hk, map_b);
+            tma_load_4d(vdst + off, &tmap_v, full(s), 64 * pn, tok, hk, map_b);
           }
         }
       }
@@ -443,7 +452,7 @@ decode_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
         const int vp = v0 + lane;
         if (vp < c_end) {
           const int tok = km.to_token(v0 & ~(kBoxTok - 1)) + (lane & (kBoxTok - 1));
-          ok = tok >= 0 && tok < km.len;
+          ok = tok >= 0 && (km.mode == kPaged || tok < km.len);
         }
       }
       const unsigned vmask = __ballot_sync(0xffffffffu, ok) & 0xffffu;
@@ -603,6 +612,10 @@ static int decode_max_visible(const b200attn_decode_args* a) {
     return (int)(w < a->max_seqlen ? w : a->max_seqlen);
   }
   if (a->sparsity == B200ATTN_BLOCK_LIST) return a->max_sel * a->block_size;
+  if (a->sparsity == kPaged) {
+    long long w = (long long)a->max_sel * a->block_size;
+    return (int)(w < a->max_seqlen ? w : a->max_seqlen);
+  }
   return a->max_seqlen;
 }
 
@@ -630,7 +643,7 @@ size_t decode_workspace_bytes(const b200attn_decode_args* a) {
   return (size_t)(rows * a->head_dim * 4 + rows * 4);
 }
 
-static int validate_decode(const b200attn_decode_args* a, bool sparse) {
+static int validate_decode(const b200attn_decode_args* a, bool sparse, bool paged) {
   if (!a || !a->q || !a->k_cache || !a->v_cache || !a->o) return B200ATTN_ERR_NULL;
   if (!a->cu_seqlens == !a->seqlens) return B200ATTN_ERR_NULL;  // exactly one of the two
   if (a->dtype != B200ATTN_F16 && a->dtype != B200ATTN_BF16) return B200ATTN_ERR_DTYPE;
@@ -653,7 +666,7 @@ static int validate_decode(const b200attn_decode_args* a, bool sparse) {
   int mode = sparse ? a->sparsity : B200ATTN_DENSE;
   if (mode == B200ATTN_WINDOW) {
     if (a->window_global < 0 || a->window_local < 0) return B200ATTN_ERR_MODE;
-  } else if (mode == B200ATTN_BLOCK_LIST) {
+  } else if (mode == B200ATTN_BLOCK_LIST || (paged && mode == kPaged)) {
     if (!a->block_idx) return B200ATTN_ERR_NULL;
     if (a->block_size <= 0 || a->block_size % 16 != 0 || a->max_sel <= 0) return B200ATTN_ERR_MODE;
   } else if (mode != B200ATTN_DENSE) {
@@ -716,19 +729,15 @@ static int launch_decode_tma_d(const b200attn_decode_args* a, const DecodeParams
                                cudaStream_t stream) {
   using L = DecodeTmaSmem<DP>;
   CUtensorMap tk, tv;
-  // keys beyond max_seqlen are never visible; the copy engine zero-fills past that extent
-  if (!make_cache_tmap(&tk, a->dtype, a->k_cache, a->head_dim, a->max_seqlen, a->heads_kv, a->batch,
+  if (!make_cache_tmap(&tk, a->dtype, a->k_cache, a->head_dim, p.map_keys, a->heads_kv, p.map_batch,
                        a->k_stride_t, a->k_stride_h, a->k_stride_b) ||
-      !make_cache_tmap(&tv, a->dtype, a->v_cache, a->head_dim, a->max_seqlen, a->heads_kv, a->batch,
+      !make_cache_tmap(&tv, a->dtype, a->v_cache, a->head_dim, p.map_keys, a->heads_kv, p.map_batch,
                        a->v_stride_t, a->v_stride_h, a->v_stride_b))
     return B200ATTN_ERR_CUDA;
   auto kern = decode_split_tma_kernel<T, DP>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
-      return B200ATTN_ERR_CUDA;
-    attr_set = true;
-  }
+  // per device and cheap, so set on every call rather than remembered
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
+    return B200ATTN_ERR_CUDA;
   kern<<<g1, 160, L::kAlloc, stream>>>(tk, tv, p);
   switch (a->head_dim) {
     case 32: decode_combine_kernel<T, 32><<<g2, 128, 0, stream>>>(p); break;
@@ -747,9 +756,10 @@ static int launch_decode_tma(const b200attn_decode_args* a, const DecodeParams& 
 }
 
 // scratch == nullptr: use the caller's workspace from the args.
-int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t scratch_bytes,
-               cudaStream_t stream) {
-  int st = validate_decode(a, sparse);
+// pool_keys > 0: the caches are page pools of that many rows and a->sparsity is kPaged.
+static int decode_fwd_impl(const b200attn_decode_args* a, bool sparse, long long pool_keys, void* scratch,
+                           size_t scratch_bytes, cudaStream_t stream) {
+  int st = validate_decode(a, sparse, pool_keys > 0);
   if (st != B200ATTN_OK) return st;
   b200attn_decode_args eff = *a;
   if (!sparse) eff.sparsity = B200ATTN_DENSE;
@@ -778,6 +788,9 @@ int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t
   p.block_size = a->block_size; p.max_sel = a->max_sel;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.head_dim_rt = a->head_dim;
+  // keys beyond max_seqlen are never visible; the copy engine zero-fills past the extent
+  p.map_keys = pool_keys > 0 ? pool_keys : a->max_seqlen;
+  p.map_batch = pool_keys > 0 ? 1 : a->batch;
   long long rows = (long long)a->batch * a->heads_q * p.max_chunks;
   p.part_o = (float*)ws;
   p.part_lse = p.part_o + rows * a->head_dim;
@@ -797,6 +810,60 @@ int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t
   dim3 g1(a->heads_kv * p.ggroups, p.max_chunks, a->batch);
   return a->dtype == B200ATTN_F16 ? launch_decode_d<__half>(a->head_dim, p, g1, g2, stream)
                                   : launch_decode_d<__nv_bfloat16>(a->head_dim, p, g1, g2, stream);
+}
+
+int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t scratch_bytes,
+               cudaStream_t stream) {
+  if (a && sparse && a->sparsity == kPaged) return B200ATTN_ERR_MODE;   // only reachable through paged_decode_fwd
+  return decode_fwd_impl(a, sparse, 0, scratch, scratch_bytes, stream);
+}
+
+// --------------------------------------------------------------------------
+// Paged KV: the caches are pools [num_pages, page_size, heads_kv, head_dim] and a
+// page table says where the pages of each sequence are.  Page p of the pool is
+// rows p * page_size .. of a flat [num_pages * page_size] key axis, so a page
+// table is a block list over that axis that covers every key of the sequence.
+// --------------------------------------------------------------------------
+static int paged_as_decode_args(const b200attn_paged_decode_args* g, b200attn_decode_args* a) {
+  if (!g) return B200ATTN_ERR_NULL;
+  if (!g->page_table || !g->seqlens) return B200ATTN_ERR_NULL;
+  if (g->page_size <= 0 || g->page_size % 16 != 0 || g->num_pages <= 0 || g->max_pages_per_seq <= 0)
+    return B200ATTN_ERR_MODE;
+  if (g->k_stride_page != (int64_t)g->page_size * g->k_stride_t ||
+      g->v_stride_page != (int64_t)g->page_size * g->v_stride_t)
+    return B200ATTN_ERR_STRIDE;   // pages must follow one another on the key axis
+  *a = b200attn_decode_args{};
+  a->q = g->q; a->k_cache = g->k_pages; a->v_cache = g->v_pages; a->o = g->o;
+  a->dtype = g->dtype;
+  a->batch = g->batch; a->heads_q = g->heads_q; a->heads_kv = g->heads_kv; a->head_dim = g->head_dim;
+  a->max_seqlen = g->max_seqlen;
+  a->seqlens = g->seqlens;
+  a->q_stride_b = g->q_stride_b; a->q_stride_h = g->q_stride_h;
+  a->k_stride_b = 0; a->k_stride_t = g->k_stride_t; a->k_stride_h = g->k_stride_h;
+  a->v_stride_b = 0; a->v_stride_t = g->v_stride_t; a->v_stride_h = g->v_stride_h;
+  a->o_stride_b = g->o_stride_b; a->o_stride_h = g->o_stride_h;
+  a->softmax_scale = g->softmax_scale;
+  a->chunk_tokens = g->chunk_tokens;
+  a->sparsity = kPaged;
+  a->block_idx = g->page_table;
+  a->block_size = g->page_size;
+  a->max_sel = g->max_pages_per_seq;
+  a->workspace = g->workspace; a->workspace_bytes = g->workspace_bytes;
+  a->status_word = g->status_word;
+  return B200ATTN_OK;
+}
+
+size_t paged_decode_workspace_bytes(const b200attn_paged_decode_args* g) {
+  b200attn_decode_args a;
+  if (paged_as_decode_args(g, &a) != B200ATTN_OK) return 0;
+  return decode_workspace_bytes(&a);
+}
+
+int paged_decode_fwd(const b200attn_paged_decode_args* g, cudaStream_t stream) {
+  b200attn_decode_args a;
+  int st = paged_as_decode_args(g, &a);
+  if (st != B200ATTN_OK) return st;
+  return decode_fwd_impl(&a, true, (long long)g->num_pages * g->page_size, nullptr, 0, stream);
 }
 
 // --------------------------------------------------------------------------

@@ -11,8 +11,9 @@ import torch
 from torch import Tensor
 
 from . import _lib
-from ._lib import (BLOCK_LIST, DENSE, WINDOW, DecodeArgs, KvAppendArgs, KvPackArgs, PrefillArgs,
-                   PrefillBwdArgs)
+from ._lib import (BLOCK_LIST, DENSE, WINDOW, DecodeArgs, KvAppendArgs, KvPackArgs, PagedDecodeArgs,
+                   PrefillArgs, PrefillBwdArgs, TopkBlocksArgs, WindowBlocksDecodeArgs,
+                   WindowBlocksPrefillArgs)
 
 LOG2E = 1.4426950408889634
 _DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
@@ -124,6 +125,107 @@ def decode(q, k_cache, v_cache, *, cu_seqlens=None, seqlens=None, max_seqlen=Non
                       float(scale), int(chunk), int(sparsity), int(window_global),
                       int(window_local), _i32(block_idx, q.device), _i32(block_cnt, q.device),
                       int(block_size))
+
+
+def paged_decode(q: Tensor, k_pages: Tensor, v_pages: Tensor, page_table: Tensor, seqlens: Tensor, *,
+                 max_seqlen: Optional[int] = None, scale: Optional[float] = None, chunk: int = 0) -> Tensor:
+    """Split-KV GQA decoding over page pools [num_pages, page_size, Hkv, D] addressed through
+    page_table int32 [B, max_pages]; see b200attn_paged_decode_fwd in include/b200attn.h."""
+    _need_cuda(q, k_pages, v_pages, page_table, seqlens)
+    if q.dtype not in _DT or k_pages.dtype != q.dtype or v_pages.dtype != q.dtype:
+        raise ValueError("b200attn: q, k, v must share dtype float16 or bfloat16")
+    q, k, v = _rowmajor16(q), _rowmajor16(k_pages), _rowmajor16(v_pages)
+    table, sl = _i32(page_table, q.device), _i32(seqlens, q.device)
+    B, Hq, D = q.shape
+    P, page, Hkv, _ = k.shape
+    o = torch.empty(B, Hq, v.shape[3], device=q.device, dtype=q.dtype)
+    a = PagedDecodeArgs()
+    a.q, a.k_pages, a.v_pages, a.o = _ptr(q), _ptr(k), _ptr(v), _ptr(o)
+    a.dtype, a.batch, a.heads_q, a.heads_kv, a.head_dim = _DT[q.dtype], B, Hq, Hkv, D
+    a.page_size, a.num_pages, a.max_pages_per_seq = page, P, table.shape[1]
+    a.max_seqlen = int(max_seqlen) if max_seqlen is not None else table.shape[1] * page
+    a.page_table, a.seqlens = _ptr(table), _ptr(sl)
+    a.q_stride_b, a.q_stride_h = q.stride(0), q.stride(1)
+    a.k_stride_page, a.k_stride_t, a.k_stride_h = k.stride(0), k.stride(1), k.stride(2)
+    a.v_stride_page, a.v_stride_t, a.v_stride_h = v.stride(0), v.stride(1), v.stride(2)
+    a.o_stride_b, a.o_stride_h = o.stride(0), o.stride(1)
+    a.softmax_scale = float(scale) if scale is not None else D ** -0.5
+    a.chunk_tokens = int(chunk)
+    L = _lib.lib()
+    need = L.b200attn_paged_decode_workspace_bytes(C.byref(a))
+    ws = torch.empty(max(need, 16), device=q.device, dtype=torch.uint8)
+    a.workspace, a.workspace_bytes = _ptr(ws), ws.numel()
+    with torch.cuda.device(q.device):
+        _lib.check(L.b200attn_paged_decode_fwd(C.byref(a), _stream(q)))
+    _count()
+    return o
+
+
+# --------------------------------------------------------------------------
+# block selection (builders of the BLOCK_LIST inputs)
+# --------------------------------------------------------------------------
+def window_blocks_prefill(batch: int, heads: int, n_qblocks: int, window_local: int, window_global: int,
+                          *, block_size: int = 64, device="cuda") -> Tuple[Tensor, Tensor]:
+    """(block_idx [B, H, n_qblocks, max_nnz], block_cnt [B, H, n_qblocks]): the block cover of the
+    window pattern, in the layout prefill(sparsity=BLOCK_LIST) takes."""
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError("b200attn ops take CUDA tensors only (there is no CPU path)")
+    L = _lib.lib()
+    nnz = max(1, L.b200attn_window_blocks_prefill_max_nnz(block_size, window_local, window_global, n_qblocks))
+    idx = torch.empty(batch, heads, n_qblocks, nnz, device=dev, dtype=torch.int32)
+    cnt = torch.empty(batch, heads, n_qblocks, device=dev, dtype=torch.int32)
+    a = WindowBlocksPrefillArgs(_ptr(idx), _ptr(cnt), batch, heads, n_qblocks, nnz, block_size,
+                                window_local, window_global)
+    with torch.cuda.device(dev):
+        _lib.check(L.b200attn_window_blocks_prefill(C.byref(a), _stream(idx)))
+    _count()
+    return idx, cnt
+
+
+def window_blocks_decode(seqlens: Tensor, heads_kv: int, window_local: int, window_global: int, *,
+                         block_size: int = 64, max_sel: Optional[int] = None) -> Tuple[Tensor, Tensor]:
+    """(block_idx [B, Hkv, max_sel], block_cnt [B, Hkv]): the blocks holding the sink and recent
+    keys of each sequence, in the layout decode(sparsity=BLOCK_LIST) takes."""
+    _need_cuda(seqlens)
+    sl = _i32(seqlens, seqlens.device)
+    B = sl.numel()
+    if max_sel is None:
+        max_sel = (window_global + block_size - 1) // block_size + (window_local + block_size - 2) // block_size + 1
+    max_sel = max(1, int(max_sel))
+    idx = torch.empty(B, heads_kv, max_sel, device=sl.device, dtype=torch.int32)
+    cnt = torch.empty(B, heads_kv, device=sl.device, dtype=torch.int32)
+    a = WindowBlocksDecodeArgs(_ptr(idx), _ptr(cnt), None, _ptr(sl), B, heads_kv, max_sel, block_size,
+                               window_local, window_global)
+    with torch.cuda.device(sl.device):
+        _lib.check(_lib.lib().b200attn_window_blocks_decode(C.byref(a), _stream(sl)))
+    _count()
+    return idx, cnt
+
+
+def topk_blocks(scores: Tensor, top_k: int, *, n_valid: Optional[Tensor] = None, force_first: int = 0,
+                force_last: int = 0) -> Tuple[Tensor, Tensor]:
+    """Per row of fp32 `scores` [..., n_blocks]: the top_k best candidate blocks in ascending block
+    order, (block_idx [..., top_k] padded with -1, block_cnt [...])."""
+    _need_cuda(scores, n_valid)
+    if scores.dtype != torch.float32:
+        raise ValueError("b200attn: block scores must be float32")
+    lead = scores.shape[:-1]
+    s2 = scores.reshape(-1, scores.shape[-1])
+    if s2.stride(-1) != 1:
+        s2 = s2.contiguous()
+    rows, n = s2.shape
+    nv = _i32(n_valid, scores.device)
+    if nv is not None and nv.numel() != rows:
+        raise ValueError("b200attn: n_valid needs one entry per row of scores")
+    idx = torch.empty(rows, top_k, device=scores.device, dtype=torch.int32)
+    cnt = torch.empty(rows, device=scores.device, dtype=torch.int32)
+    a = TopkBlocksArgs(_ptr(s2), s2.stride(0), _ptr(nv), rows, n, top_k, force_first, force_last,
+                       _ptr(idx), _ptr(cnt))
+    with torch.cuda.device(scores.device):
+        _lib.check(_lib.lib().b200attn_topk_blocks(C.byref(a), _stream(scores)))
+    _count()
+    return idx.reshape(*lead, top_k), cnt.reshape(lead)
 
 
 # --------------------------------------------------------------------------
