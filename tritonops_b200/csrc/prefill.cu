@@ -9,8 +9,7 @@
 //   warp 9   TMA producer: Q tiles, then K_0, V_0, K_1, V_1, ... into a ring of
 //            128-byte-swizzled shared-memory stages (mbarrier full/empty pairs)
 //   warp 8   MMA issuer (one thread): S_t = Q_t K_j^T and O_t += P_t V_j with
-//            tcgen05.mma; S, P and O live in tensor memory (TMEM).  In the dense /
-//            window kernel warp 8 issues tile 0 and warp 10 tile 1, in 64-key half steps
+//            tcgen05.mma; S, P and O live in tensor memory (TMEM)
 //   warps 0-3 / 4-7   softmax warpgroup of tile 0 / tile 1: one thread per query
 //            row reads its S row from TMEM, keeps the running max and sum in
 //            registers (base-2 exponentials), writes P back over S as packed
@@ -31,21 +30,15 @@ using namespace sm100;
 
 constexpr int kMmaWarp = 8;
 constexpr int kLoadWarp = 9;
-constexpr int kMmaWarp2 = 10;   // dense / window kernel: products of query tile 1 (warp 8 then has tile 0)
 constexpr int kPrefillThreads = 384;        // warps 10, 11 only complete the third warpgroup
-// Registers per thread after setmaxnreg: the softmax warps (8) of the block-list
-// kernel hold a 128-column score row, those of the dense / window kernel a
-// 64-column half row, which leaves the MMA / TMA / idle warps (4) enough to keep
-// their loop state out of local memory.
-constexpr int kSoftmaxRegs = 216, kOtherRegs = 72;            // block list
-constexpr int kSoftmaxRegsHalf = 192, kOtherRegsHalf = 120;   // dense / window
+constexpr int kSoftmaxRegs = 216;           // per thread, after setmaxnreg (8 warps)
+constexpr int kOtherRegs = 72;              // MMA / TMA / idle warps
 // setmaxnreg.inc can only take registers that setmaxnreg.dec of the same CTA
 // released, so with R registers per thread at launch the budgets must satisfy
 // 128 (R - kOtherRegs) >= 256 (kSoftmaxRegs - R); R = 168 is what 384 threads
 // per CTA allow.  The launcher refuses to run a build whose R is smaller.
 constexpr int kLaunchRegs = 168;
-static_assert(128 * (kLaunchRegs - kOtherRegs) >= 256 * (kSoftmaxRegs - kLaunchRegs) &&
-              128 * (kLaunchRegs - kOtherRegsHalf) >= 256 * (kSoftmaxRegsHalf - kLaunchRegs),
+static_assert(128 * (kLaunchRegs - kOtherRegs) >= 256 * (kSoftmaxRegs - kLaunchRegs),
               "setmaxnreg budgets would deadlock");
 constexpr int kTileM = 128;            // query rows per tile
 constexpr int kPairM = 2 * kTileM;     // query rows per CTA
@@ -116,28 +109,27 @@ __device__ __forceinline__ bool tile_needs_mask(const PrefillParams& p, int q0t,
 }
 
 #ifdef B200ATTN_TRACE
-// Debug builds only: event trace (event id, SM clock) of one heavy CTA.  Every
-// tracing thread appends to its own warp's slice, so an event costs one store.
-constexpr int kTraceSlice = 4096;
-__device__ unsigned long long g_trace[12 * kTraceSlice];
-__device__ __forceinline__ void trace_ev(int id, unsigned& n) {
+// Debug builds only: event trace (event id, SM clock) of one heavy CTA.
+__device__ unsigned int g_trace_n;
+__device__ unsigned long long g_trace[1 << 16];
+__device__ __forceinline__ void trace_ev(int id) {
   if (blockIdx.x != 16 * 40) return;   // one CTA with the longest KV loop
   long long c;
   asm volatile("mov.u64 %0, %%clock64;" : "=l"(c)::"memory");
-  if (n < kTraceSlice) g_trace[(threadIdx.x >> 5) * kTraceSlice + n] = ((unsigned long long)id << 48) | ((unsigned long long)c & 0xffffffffffffULL);
-  ++n;
+  unsigned int i = atomicAdd(&g_trace_n, 1u);
+  if (i < (1u << 16)) g_trace[i] = ((unsigned long long)id << 48) | ((unsigned long long)c & 0xffffffffffffULL);
 }
-#define TRACE(id) trace_ev(id, trace_n)
-#define TRACE_DECL unsigned trace_n = 0
+#define TRACE(id) trace_ev(id)
 extern "C" int b200attn_debug_read_trace(unsigned long long* host_out, int count) {
+  unsigned int n = 0;
+  cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(n));
   cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * count);
-  static unsigned long long zeros[12 * kTraceSlice];
-  cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros));
-  return count;
+  unsigned int zero = 0;
+  cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));
+  return (int)n;
 }
 #else
 #define TRACE(id) do {} while (0)
-#define TRACE_DECL do {} while (0)
 #endif
 
 __device__ __forceinline__ float ex2(float x) {
@@ -183,7 +175,7 @@ struct PrefillSmem {
   static constexpr int kStageBytes = BN * DP * 2;
   static constexpr int kKvPanel = BN * 128;
   static constexpr int kBarOffset = 2 * kQBytes + NSTAGE * kStageBytes;
-  static constexpr int kNumBars = 2 + 2 * NSTAGE + 12;
+  static constexpr int kNumBars = 2 + 2 * NSTAGE + 6;
   // block-list mode: 4 bitmaps (one per 64-row query block of the CTA), then per
   // query tile the merged ascending list of KV blocks with a 2-bit membership mask
   static constexpr int kBitmapOffset = kBarOffset + kNumBars * 8 + 16;
@@ -201,7 +193,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   using L = PrefillSmem<DP, BN, NSTAGE>;
   constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   constexpr uint32_t kIdescQK = idesc_f16(kFmt, false, kTileM, BN);
-  constexpr uint32_t kIdescQKh = idesc_f16(kFmt, false, kTileM, BN / 2);
   constexpr uint32_t kIdescPV = idesc_f16(kFmt, true, kTileM, DP);
   constexpr int kPanels = DP / 64;
 
@@ -237,32 +228,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   auto q_full = [&](int t) { return bars + 8 * t; };
   auto kv_full = [&](int s) { return bars + 8 * (2 + s); };
   auto kv_empty = [&](int s) { return bars + 8 * (2 + NSTAGE + s); };
-  // S ready / P ready per (tile, 64-key half); block-list mode uses only half 0 (whole 128-key steps)
-  auto s_full2 = [&](int t, int hb) { return bars + 8 * (2 + 2 * NSTAGE + 2 * t + hb); };
-  auto p_full2 = [&](int t, int hb) { return bars + 8 * (6 + 2 * NSTAGE + 2 * t + hb); };
-  auto s_full = [&](int t) { return s_full2(t, 0); };
-  auto p_full = [&](int t) { return p_full2(t, 0); };
-  // P V products done, per (tile, half): a waiter may lag a barrier by one phase only, and the
-  // softmax warpgroup runs up to two half steps ahead of the products
-  auto o_full2 = [&](int t, int hb) { return bars + 8 * (10 + 2 * NSTAGE + 2 * t + hb); };
-  auto o_full = [&](int t) { return o_full2(t, 0); };
+  auto s_full = [&](int t) { return bars + 8 * (2 + 2 * NSTAGE + t); };
+  auto p_full = [&](int t) { return bars + 8 * (4 + 2 * NSTAGE + t); };
+  auto o_full = [&](int t) { return bars + 8 * (6 + 2 * NSTAGE + t); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kBarOffset + L::kNumBars * 8 + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  TRACE_DECL;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int t = 0; t < 2; ++t) {
       mbar_init(q_full(t), 1);
-      for (int hb = 0; hb < 2; ++hb) {
-        mbar_init(s_full2(t, hb), 1);
-        mbar_init(p_full2(t, hb), kTileM);
-        mbar_init(o_full2(t, hb), 1);
-      }
+      mbar_init(s_full(t), 1);
+      mbar_init(p_full(t), kTileM);
+      mbar_init(o_full(t), 1);
     }
-    // a stage is free again when every MMA warp that reads it has released it
-    for (int s = 0; s < NSTAGE; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), BLK ? 1 : 2); }
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -352,7 +333,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
   if (warp >= 8) {
     // third warpgroup: TMA producer, MMA issuer and two idle warps give registers away
-    setmaxnreg_dec<BLK ? kOtherRegs : kOtherRegsHalf>();
+    setmaxnreg_dec<kOtherRegs>();
     if (warp == kLoadWarp) {
     // ================================================================= TMA
     {
@@ -413,7 +394,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       for (int c = max(cnt - NSTAGE, 0); c < cnt; ++c)
         mbar_wait(kv_full(c % NSTAGE), (c / NSTAGE) & 1, abort_flag);
     }
-    } else if (warp == kMmaWarp || (!BLK && warp == kMmaWarp2)) {
+    } else if (warp == kMmaWarp) {
     // ================================================================= MMA
     // The whole warp walks the loop in lock step and every lane executes the
     // (predicated) MMA instructions; only `issue`'s lane really issues them, so
@@ -457,63 +438,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         ++pv_cnt[t];
       };
       if (!blk) {
-        // Both tiles share every K/V stage.  Each tile's 128-key step is split into two
-        // 64-key halves with their own S columns and barriers: while the softmax
-        // warpgroup works on one half, the tensor core multiplies the other half's
-        // P with V and computes that half's next scores, so neither side waits for a
-        // whole step of the other.
-        // This warp issues the products of one query tile (warp 8: tile 0, warp 10:
-        // tile 1); two warps because the scalar code between two batches competes
-        // with the softmax warps of its scheduler for issue slots while the tensor
-        // pipe's short queue drains.  All of it is indexed by compile-time constants
-        // and kept in registers.
-        const int t = warp == kMmaWarp ? 0 : 1;
-        const uint32_t tSt = tS(t), tOt = tO(t);
-        uint64_t dqa[8];   // A descriptors of the eight 16-wide steps over head_dim
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          dqa[ks] = dq0 + (uint64_t)((t * L::kQBytes + (ks / 4) * L::kQPanel + (ks % 4) * 32) >> 4);
-        int done = 0;      // active steps of this tile whose products are issued
-        auto issue_qk_h = [&](int hb, int s) {
-          const uint64_t db = dk0 + (uint64_t)((s * L::kStageBytes + hb * (BN / 2) * 128) >> 4);
-          if (DP == 128)
-            mma_ss_x8_a(tSt + 64u * hb, dqa, (uint32_t)db, (uint32_t)(db >> 32), kIdescQKh, issue);
-          else
-            mma_ss_x4(tSt + 64u * hb, (uint32_t)dqa[0], (uint32_t)(dqa[0] >> 32), (uint32_t)db, (uint32_t)(db >> 32), kIdescQKh, issue);
-          mma_commit(s_full2(t, hb), issue);
-          if (issue) TRACE(80 + 2 * t + hb);
-        };
-        auto issue_pv_h = [&](int hb, int s) {
-          mbar_wait(p_full2(t, hb), done & 1, abort_flag);
-          tc_fence_after();
-          if (issue) TRACE(10 + 2 * t + hb);
-          const uint64_t db = dv0 + (uint64_t)((s * L::kStageBytes + hb * (BN / 2 / 16) * 2048) >> 4);
-          mma_ts_x4(tOt, tSt + 64u * hb, (uint32_t)db, (uint32_t)(db >> 32), kIdescPV,
-                    (done > 0 || hb > 0) ? 1u : 0u, issue);
-          mma_commit(o_full2(t, hb), issue);
-          if (issue) TRACE(20 + 2 * t + hb);
-        };
-        bool act = n_steps > 0 && step_active(t, 0);
-        if (n_steps > 0) {
-          if (q0 + kTileM * t < len) { mbar_wait(q_full(t), 0, abort_flag); tc_fence_after(); }
-          const int sK = wait_stage();
-          if (act) { issue_qk_h(0, sK); issue_qk_h(1, sK); }
-          mma_commit(kv_empty(sK), issue);
-        }
+        // both tiles share every K/V stage
+        int sK = n_steps > 0 ? wait_stage() : 0;
+        for (int t = 0; t < 2; ++t)
+          if (n_steps > 0 && step_active(t, 0)) issue_qk(t, sK);
+        if (n_steps > 0) mma_commit(kv_empty(sK), issue);
         for (int j = 0; j < n_steps; ++j) {
           const int sV = wait_stage();
           const bool more = j + 1 < n_steps;
-          const int sKn = more ? wait_stage() : 0;
-          const bool actn = more && step_active(t, j + 1);
-#pragma unroll
-          for (int hb = 0; hb < 2; ++hb) {
-            if (act) issue_pv_h(hb, sV);
-            if (actn) issue_qk_h(hb, sKn);
+          int sKn = 0;
+          for (int t = 0; t < 2; ++t) {
+            if (step_active(t, j)) issue_pv(t, sV);
+            if (t == 1) mma_commit(kv_empty(sV), issue);
+            if (more) {
+              if (t == 0) sKn = wait_stage();
+              if (step_active(t, j + 1)) issue_qk(t, sKn);
+              if (t == 1) mma_commit(kv_empty(sKn), issue);
+            }
           }
-          mma_commit(kv_empty(sV), issue);
-          if (more) mma_commit(kv_empty(sKn), issue);
-          done += act;
-          act = actn;
         }
       } else {
         // block lists: each tile consumes its own stages (same order as the loader)
@@ -531,7 +473,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     }
   } else {
     // ============================================================= softmax
-    setmaxnreg_inc<BLK ? kSoftmaxRegs : kSoftmaxRegsHalf>();
+    setmaxnreg_inc<kSoftmaxRegs>();
     const int t = warp >> 2;                       // query tile of this warpgroup
     const int row = threadIdx.x & (kTileM - 1);    // row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
@@ -541,105 +483,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     float m_run = -INFINITY;  // max the stored P / O are relative to (raw score units)
     float l_run = 0.f;
     int items = 0;
-    int steps_done = 0;   // dense / window: 128-key steps (two items each)
     if (q0t < len) {
-      if constexpr (!BLK) {
-      // dense / window: 64-key half steps (see the MMA warp)
-      constexpr int HB = BN / 2;
-      for (int j = 0; j < n_steps; ++j) {
-        if (!step_active(t, j)) continue;
-        const int kvt = seq.kv(j);
-        const bool need_mask = tile_needs_mask<BN>(p, q0t, len, kvt);
-#pragma unroll 1
-        for (int hb = 0; hb < 2; ++hb) {
-          mbar_wait(s_full2(t, hb), steps_done & 1, abort_flag);
-          tc_fence_after();
-          if (row == 0) TRACE(30 + 2 * t + hb);
-          uint32_t sr[HB];
-#pragma unroll
-          for (int cc = 0; cc < HB / 32; ++cc) tmem_ld32(tS(t) + lane_off + HB * hb + 32 * cc, &sr[32 * cc]);
-          tmem_wait_ld();
-          if (row == 0) TRACE(40 + 2 * t + hb);
-          if (need_mask) {
-            // Column x of this half is visible iff x < lim and (x >= lo or x < gl):
-            // lim from the causal diagonal and the sequence end, lo from the local
-            // window, gl from the global prefix.  Kept to a compare + select per
-            // element: this code runs once or twice per CTA, so its size (cold
-            // instruction fetches) matters more than its issue count.
-            const int kv0 = kvt * BN + HB * hb;
-            int lim = len - kv0;
-            if (p.causal) lim = min(lim, qi - kv0 + 1);
-            if (!p.window) {
-#pragma unroll
-              for (int x = 0; x < HB; ++x)
-                if (x >= lim) sr[x] = 0xff800000u;  // -inf
-            } else {
-              const int lo = qi - p.win_local + 1 - kv0;
-              const int gl = p.win_global - kv0;
-#pragma unroll
-              for (int x = 0; x < HB; ++x)
-                if (x >= lim || (x < lo && x >= gl)) sr[x] = 0xff800000u;
-            }
-          }
-          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-          for (int x = 0; x < HB; x += 8) {
-            mx0 = fmax3(mx0, __uint_as_float(sr[x]), __uint_as_float(sr[x + 1]));
-            mx1 = fmax3(mx1, __uint_as_float(sr[x + 2]), __uint_as_float(sr[x + 3]));
-            mx2 = fmax3(mx2, __uint_as_float(sr[x + 4]), __uint_as_float(sr[x + 5]));
-            mx3 = fmax3(mx3, __uint_as_float(sr[x + 6]), __uint_as_float(sr[x + 7]));
-          }
-          const float m_new = fmax3(m_run, fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-          // keep the stale max unless it is too far behind (first half: always take)
-          const bool grow = (items == 0) || ((m_new - m_run) * c > kLazyRescaleLog2) ||
-                            (m_run == -INFINITY && m_new != -INFINITY);
-          const float m_use = grow ? m_new : m_run;
-          const float alpha = (m_use == m_run) ? 1.f : ex2((m_run - m_use) * c);
-          if (items > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-            // O_t must hold every product issued so far before it is rescaled: the latest
-            // one is the other half's (products complete in issue order)
-            if (hb == 0) mbar_wait(o_full2(t, 1), (steps_done - 1) & 1, abort_flag);
-            else mbar_wait(o_full2(t, 0), steps_done & 1, abort_flag);
-            tc_fence_after();
-#pragma unroll
-            for (int cc = 0; cc < DP / 32; ++cc) {
-              uint32_t orr[32];
-              tmem_ld32(tO(t) + lane_off + 32 * cc, orr);
-              tmem_wait_ld();
-#pragma unroll
-              for (int x = 0; x < 32; ++x) orr[x] = __float_as_uint(__uint_as_float(orr[x]) * alpha);
-              tmem_st32(tO(t) + lane_off + 32 * cc, orr);
-            }
-            tmem_wait_st();
-          }
-          const float mc = (m_use == -INFINITY) ? 0.f : m_use * c;
-          float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-          uint32_t pr[HB / 2];
-          const float neg_mc = -mc;
-#pragma unroll
-          for (int x = 0; x < HB / 2; x += 2) {
-            float e0, e1, e2, e3;
-            ffma2(e0, e1, __uint_as_float(sr[2 * x]), __uint_as_float(sr[2 * x + 1]), c, neg_mc);
-            ffma2(e2, e3, __uint_as_float(sr[2 * x + 2]), __uint_as_float(sr[2 * x + 3]), c, neg_mc);
-            e0 = ex2(e0); e1 = ex2(e1); e2 = ex2(e2); e3 = ex2(e3);
-            fadd2(sum0, sum1, e0, e1);
-            fadd2(sum2, sum3, e2, e3);
-            pr[x] = pack2<T>(e0, e1);
-            pr[x + 1] = pack2<T>(e2, e3);
-          }
-          sum0 += sum2; sum1 += sum3;
-          tmem_st32(tS(t) + lane_off + HB * hb, pr);
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(p_full2(t, hb));
-          if (row == 0) TRACE(70 + 2 * t + hb);
-          l_run = l_run * alpha + (sum0 + sum1);
-          m_run = m_use;
-          ++items;
-        }
-        ++steps_done;
-      }
-      } else {
       for (int j = 0; j < n_steps; ++j) {
         const int kvt = blk ? 0 : seq.kv(j);
         if (!step_active(t, j)) continue;
@@ -765,19 +609,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         m_run = m_use;
         ++items;
       }
-      }
       // ------------------------------------------------------- epilogue
       const bool row_ok = qi < len;
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const long long tok = (long long)seq_start + qi;
       T* orow = (T*)p.o + (p.cu_seqlens ? 0 : (long long)b * p.o_sb) + tok * p.o_st + (long long)h * p.o_sh;
       if (items > 0) {
-        if constexpr (!BLK) {
-          mbar_wait(o_full2(t, 0), (steps_done - 1) & 1, abort_flag);
-          mbar_wait(o_full2(t, 1), (steps_done - 1) & 1, abort_flag);
-        } else {
-          mbar_wait(o_full(t), (items - 1) & 1, abort_flag);
-        }
+        mbar_wait(o_full(t), (items - 1) & 1, abort_flag);
         tc_fence_after();
       }
 #pragma unroll

@@ -268,52 +268,6 @@ __device__ __forceinline__ void mma_ts_x8(uint32_t d_tmem, uint32_t a_tmem, uint
       ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(issue)
       : "memory");
 }
-// 8 SS products like mma_ss_x8 with the A descriptors of the eight steps given ready made
-// (they do not change during a kernel), so a step costs one add, one move and the product.
-__device__ __forceinline__ void mma_ss_x8_a(uint32_t d_tmem, const uint64_t (&a)[8], uint32_t b_lo, uint32_t b_hi,
-                                             uint32_t idesc, uint32_t issue) {
-  asm volatile(
-      "{\n\t.reg .pred pi, pt, pf;\n\t.reg .b64 db;\n\t.reg .b32 lb;\n\t"
-      "setp.ne.b32 pi, %12, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tsetp.ne.b32 pf, 0, 0;\n\t"
-      "mov.b64 db, {%9, %10};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], %1, db, %11, pf;\n\t"
-      "add.u32 lb, %9, 2;\n\tmov.b64 db, {lb, %10};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], %2, db, %11, pt;\n\t"
-      "add.u32 lb, %9, 4;\n\tmov.b64 db, {lb, %10};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], %3, db, %11, pt;\n\t"
-      "add.u32 lb, %9, 6;\n\tmov.b64 db, {lb, %10};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], %4, db, %11, pt;\n\t"
-      "add.u32 lb, %9, 1024;\n\tmov.b64 db, {lb, %10};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], %5, db, %11, pt;\n\t"
-      "add.u32 lb, %9, 1026;\n\tmov.b64 db, {lb, %10};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], %6, db, %11, pt;\n\t"
-      "add.u32 lb, %9, 1028;\n\tmov.b64 db, {lb, %10};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], %7, db, %11, pt;\n\t"
-      "add.u32 lb, %9, 1030;\n\tmov.b64 db, {lb, %10};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], %8, db, %11, pt;\n\t"
-      "}"
-      ::"r"(d_tmem), "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(a[4]), "l"(a[5]), "l"(a[6]), "l"(a[7]),
-        "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(issue)
-      : "memory");
-}
-// 4 back-to-back TS products over 64 keys (half of mma_ts_x8).
-__device__ __forceinline__ void mma_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
-                                           uint32_t idesc, uint32_t accumulate, uint32_t issue) {
-  asm volatile(
-      "{\n\t.reg .pred pi, pt, pa;\n\t.reg .b64 db;\n\t.reg .b32 ta, lb;\n\t"
-      "setp.ne.b32 pi, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tsetp.ne.b32 pa, %5, 0;\n\t"
-      "add.u32 ta, %1, 0;\n\tadd.u32 lb, %2, 0;\n\tmov.b64 db, {lb, %3};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pa;\n\t"
-      "add.u32 ta, %1, 8;\n\tadd.u32 lb, %2, 128;\n\tmov.b64 db, {lb, %3};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
-      "add.u32 ta, %1, 16;\n\tadd.u32 lb, %2, 256;\n\tmov.b64 db, {lb, %3};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
-      "add.u32 ta, %1, 24;\n\tadd.u32 lb, %2, 384;\n\tmov.b64 db, {lb, %3};\n\t"
-      "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
-      "}"
-      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(issue)
-      : "memory");
-}
 // Arrive once on `bar` when every tcgen05 operation the issuing lane started so far is done.
 __device__ __forceinline__ void mma_commit(uint32_t bar, uint32_t issue) {
   asm volatile(
