@@ -55,6 +55,25 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
+#ifdef B200ATTN_TRACE
+// Debug builds only: (event id, SM clock) of one CTA, one slice per warp.
+constexpr int kBwdTraceSlice = 4096;
+__device__ unsigned long long g_bwd_trace[5 * kBwdTraceSlice];
+__device__ __forceinline__ void bwd_trace_ev(int id, unsigned& n) {
+  if (blockIdx.x != 0 || blockIdx.y != 3 || blockIdx.z != 1) return;   // a CTA with the longest walk
+  long long c;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(c)::"memory");
+  if (n < kBwdTraceSlice)
+    g_bwd_trace[(threadIdx.x >> 5) * kBwdTraceSlice + n] = ((unsigned long long)id << 48) | ((unsigned long long)c & 0xffffffffffffULL);
+  ++n;
+}
+#define BTRACE(id) bwd_trace_ev(id, trace_n)
+#define BTRACE_DECL unsigned trace_n = 0
+#else
+#define BTRACE(id) do {} while (0)
+#define BTRACE_DECL do {} while (0)
+#endif
+
 template <int DP>
 struct BwdSmem {
   static constexpr int kOperand = kT * DP * 2;       // K, V, Q, dO tiles
@@ -62,8 +81,12 @@ struct BwdSmem {
   static constexpr int kPds = kT * kT * 2;           // P, dS tiles
   static constexpr int kK = 0, kV = kOperand, kQ = 2 * kOperand, kDO = 3 * kOperand;
   static constexpr int kP = 4 * kOperand, kDS = kP + kPds;
-  static constexpr int kBarOffset = kDS + kPds;
-  static constexpr int kNumBars = 6;
+  static constexpr int kQ1 = kDS + kPds;             // second Q tile (query tiles are double buffered)
+  static constexpr int kStage = kP;                  // fp32 dQ tile on its way to global memory: reuses P, dS
+  static constexpr int kStagePanel = kT * 128;       // 32 fp32 columns of 128 rows, 128-byte swizzle
+  static_assert((DP / 32) * kStagePanel <= 2 * kPds, "dQ staging fits in the P and dS tiles");
+  static constexpr int kBarOffset = kQ1 + kOperand;
+  static constexpr int kNumBars = 9;
   static constexpr int kBytes = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kAlloc = kBytes + 1024;
 };
@@ -72,7 +95,7 @@ template <typename T, int DP>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
            const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-           const BwdParams p) {
+           const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
   using L = BwdSmem<DP>;
   constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   constexpr uint32_t kIdSS = idesc_f16(kFmt, false, kT, kT);           // S, dP: A, B K-major
@@ -98,16 +121,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t bars = sbase + L::kBarOffset;
-  const uint32_t bar_kv = bars, bar_load = bars + 8, bar_sdp = bars + 16, bar_pds = bars + 24,
-                 bar_dq = bars + 32, bar_free = bars + 40;
+  const uint32_t bar_kv = bars, bar_q0 = bars + 8, bar_do = bars + 24, bar_sdp = bars + 32, bar_pds = bars + 40,
+                 bar_dv = bars + 48, bar_dq = bars + 56, bar_free = bars + 64;   // bar_q0 + 8: second Q buffer
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kBarOffset + L::kNumBars * 8 + 4);
 
   const int warp = threadIdx.x >> 5;
+  BTRACE_DECL;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar_kv, 1);
-    mbar_init(bar_load, 1);
+    mbar_init(bar_q0, 1);
+    mbar_init(bar_q0 + 8, 1);
+    mbar_init(bar_do, 1);
+    mbar_init(bar_dv, 1);
     mbar_init(bar_sdp, 1);
     mbar_init(bar_pds, kT);
     mbar_init(bar_dq, 1);
@@ -138,7 +165,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       }
     }
     __syncwarp();
-    const uint64_t d_q = smem_desc_sw128(sbase + L::kQ, 16, 1024);
     const uint64_t d_k = smem_desc_sw128(sbase + L::kK, 16, 1024);
     const uint64_t d_v = smem_desc_sw128(sbase + L::kV, 16, 1024);
     const uint64_t d_do = smem_desc_sw128(sbase + L::kDO, 16, 1024);
@@ -146,24 +172,45 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     const uint64_t d_ds_mn = smem_desc_sw128(sbase + L::kDS, L::kPanel, 1024);
     const uint64_t d_ds_k = smem_desc_sw128(sbase + L::kDS, 16, 1024);           // same bytes, M = q
     const uint64_t d_do_mn = smem_desc_sw128(sbase + L::kDO, L::kPanel, 1024);   // [q][d] read with K = q
-    const uint64_t d_q_mn = smem_desc_sw128(sbase + L::kQ, L::kPanel, 1024);
     const uint64_t d_k_mn = smem_desc_sw128(sbase + L::kK, L::kPanel, 1024);     // [k][d] read with K = k
-    for (int it = 0; it < n_iter; ++it) {
-      const int g = it % p.group, i = i_first + it / p.group;
-      const int hq = hk * p.group + g;
-      // the previous pair's P, dS, Q, dO and the S / dP / dQ columns are free again
-      if (it > 0) mbar_wait(bar_free, (it - 1) & 1, abort_flag);
+    // query tile and head of pair `it`
+    auto pair_of = [&](int it, int& i, int& hq) { i = i_first + it / p.group; hq = hk * p.group + it % p.group; };
+    auto load_q = [&](int it) {        // into buffer it & 1
+      int i, hq;
+      pair_of(it, i, hq);
+      const uint32_t dst = sbase + ((it & 1) ? L::kQ1 : L::kQ), bar = bar_q0 + 8 * (it & 1);
       if (issue) {
-        mbar_expect_tx(bar_load, 2 * L::kOperand);
-        for (int pn = 0; pn < kPanels; ++pn) {
-          tma_load_4d(sbase + L::kQ + pn * L::kPanel, &tmap_q, bar_load, 64 * pn, seq_start + i * kT, hq, bcoord);
-          tma_load_4d(sbase + L::kDO + pn * L::kPanel, &tmap_do, bar_load, 64 * pn, seq_start + i * kT, hq, bcoord);
-        }
+        mbar_expect_tx(bar, L::kOperand);
+        for (int pn = 0; pn < kPanels; ++pn)
+          tma_load_4d(dst + pn * L::kPanel, &tmap_q, bar, 64 * pn, seq_start + i * kT, hq, bcoord);
       }
       __syncwarp();
+    };
+    auto load_do = [&](int it) {
+      int i, hq;
+      pair_of(it, i, hq);
+      if (issue) {
+        mbar_expect_tx(bar_do, L::kOperand);
+        for (int pn = 0; pn < kPanels; ++pn)
+          tma_load_4d(sbase + L::kDO + pn * L::kPanel, &tmap_do, bar_do, 64 * pn, seq_start + i * kT, hq, bcoord);
+      }
+      __syncwarp();
+    };
+    if (n_iter > 0) { load_q(0); load_do(0); }
+    for (int it = 0; it < n_iter; ++it) {
+      int i, hq;
+      pair_of(it, i, hq);
+      // The other Q buffer was last read by pair it - 1, whose products are complete
+      // (its dQ tile has been taken out of TMEM): fetch the next query tile now.
+      if (it + 1 < n_iter) load_q(it + 1);
+      const uint32_t q_off = (it & 1) ? L::kQ1 : L::kQ;
+      const uint64_t d_q = smem_desc_sw128(sbase + q_off, 16, 1024);
+      const uint64_t d_q_mn = smem_desc_sw128(sbase + q_off, L::kPanel, 1024);
       if (it == 0) mbar_wait(bar_kv, 0, abort_flag);
-      mbar_wait(bar_load, it & 1, abort_flag);
+      mbar_wait(bar_q0 + 8 * (it & 1), (it >> 1) & 1, abort_flag);
+      mbar_wait(bar_do, it & 1, abort_flag);
       tc_fence_after();
+      if (issue) BTRACE(3);
       // S = Q K^T, dP = dO V^T
 #pragma unroll
       for (int ks = 0; ks < DP / 16; ++ks) {
@@ -175,16 +222,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         const uint64_t off = (uint64_t)(((ks / 4) * L::kPanel + (ks % 4) * 32) >> 4);
         mma_ss(tDP, d_do + off, d_v + off, kIdSS, ks > 0, issue);
       }
+      // the previous pair's dQ tile must have left the P / dS bytes before they are rewritten
+      if (issue) bulk_wait_read_all();
+      __syncwarp();
       mma_commit(bar_sdp, issue);
+      if (issue) BTRACE(4);
       // wait for P and dS in shared memory
       mbar_wait(bar_pds, it & 1, abort_flag);
       tc_fence_after();
+      if (issue) BTRACE(5);
       const uint32_t acc = it > 0 ? 1u : 0u;
 #pragma unroll
       for (int ks = 0; ks < kT / 16; ++ks) {   // contraction over the 128 queries
         const uint64_t off = (uint64_t)((ks * 2048) >> 4);
         mma_ss(tDV, d_p_mn + off, d_do_mn + off, kIdTT, ks > 0 ? 1u : acc, issue);
       }
+      mma_commit(bar_dv, issue);
 #pragma unroll
       for (int ks = 0; ks < kT / 16; ++ks) {
         const uint64_t off = (uint64_t)((ks * 2048) >> 4);
@@ -197,7 +250,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         mma_ss(tS, d_ds_k + offa, d_k_mn + offb, kIdDQ, ks > 0, issue);
       }
       mma_commit(bar_dq, issue);
+      if (issue) BTRACE(6);
+      // dO is last read by the dV product: fetch the next pair's while dK and dQ run
+      mbar_wait(bar_dv, it & 1, abort_flag);
+      if (it + 1 < n_iter) load_do(it + 1);
+      // the compute warps have moved the scaled dQ tile into shared memory: add it to the
+      // fp32 accumulator in global memory (rows past the sequence end hold exact zeros)
+      mbar_wait(bar_free, it & 1, abort_flag);
+      if (issue) BTRACE(2);
+      if (issue) {
+        const int tl0 = (p.cu_seqlens ? seq_start : b * p.seqlen) + i * kT;
+        for (int pn = 0; pn < DP / 32; ++pn)
+          tma_reduce_add_3d(&tmap_dq, sbase + L::kStage + pn * L::kStagePanel, 32 * pn, tl0, hq);
+        bulk_commit_group();
+      }
+      __syncwarp();
     }
+    if (issue) bulk_wait_all();
+    __syncwarp();
   } else {
     // ============================================ compute warps: one thread per row
     const int row = threadIdx.x;                         // query row in the tile / key row in the epilogue
@@ -219,8 +289,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         const long long tl = p.cu_seqlens ? tok : (long long)b * p.seqlen + qi;
         dsum = p.dvec[tl * p.heads_q + hq];
       }
+      if (threadIdx.x == 0) BTRACE(10);
       mbar_wait(bar_sdp, it & 1, abort_flag);
       tc_fence_after();
+      if (threadIdx.x == 0) BTRACE(11);
       // visible keys of this row inside the tile: columns [0, lim)
       int lim = live ? min(kT, len - kv0) : 0;
       if (p.causal) lim = min(lim, qi - kv0 + 1);
@@ -235,10 +307,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         for (int x = 0; x < 32; x += 2) {
           float p0 = ex2f(fmaf(__uint_as_float(sr[x]), p.scale_log2, -lse2));
           float p1 = ex2f(fmaf(__uint_as_float(sr[x + 1]), p.scale_log2, -lse2));
-          if (32 * cc + x >= lim) p0 = 0.f;
-          if (32 * cc + x + 1 >= lim) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(dr[x]) - dsum);
-          const float d1 = p1 * (__uint_as_float(dr[x + 1]) - dsum);
+          float d0 = p0 * (__uint_as_float(dr[x]) - dsum);
+          float d1 = p1 * (__uint_as_float(dr[x + 1]) - dsum);
+          // masked entries are exact zeros whatever S and dP hold there
+          if (32 * cc + x >= lim) { p0 = 0.f; d0 = 0.f; }
+          if (32 * cc + x + 1 >= lim) { p1 = 0.f; d1 = 0.f; }
           pp[x / 2] = pack2<T>(p0, p1);
           dd[x / 2] = pack2<T>(d0, d1);
         }
@@ -254,27 +327,31 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       fence_proxy_async();       // generic-proxy writes -> visible to the tensor core's reads
       tc_fence_before();
       mbar_arrive(bar_pds);
+      if (threadIdx.x == 0) BTRACE(12);
       // dQ tile of this pair -> fp32 accumulator
       mbar_wait(bar_dq, it & 1, abort_flag);
       tc_fence_after();
-      const long long tl = p.cu_seqlens ? tok : (long long)b * p.seqlen + qi;
-      float* qacc = p.dq_acc + (tl * p.heads_q + hq) * DP;
+      if (threadIdx.x == 0) BTRACE(13);
+      // scaled fp32 tile -> shared memory in the copy engine's 128-byte-swizzled layout
+      // (one panel per 32 columns); the control warp adds it to global memory
+      uint8_t* sStage = sgen + L::kStage;
 #pragma unroll
       for (int cc = 0; cc < DP / 32; ++cc) {
         uint32_t qr[32];
         tmem_ld32(tS + lane_off + 32 * cc, qr);
         tmem_wait_ld();
-        if (row_ok) {
 #pragma unroll
-          for (int x = 0; x < 32; x += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(qacc + 32 * cc + x),
-                         "f"(__uint_as_float(qr[x]) * p.scale), "f"(__uint_as_float(qr[x + 1]) * p.scale),
-                         "f"(__uint_as_float(qr[x + 2]) * p.scale), "f"(__uint_as_float(qr[x + 3]) * p.scale)
-                         : "memory");
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint32_t off = cc * L::kStagePanel + row * 128 + ((ch ^ (row & 7)) << 4);
+          *reinterpret_cast<float4*>(sStage + off) =
+              make_float4(__uint_as_float(qr[4 * ch]) * p.scale, __uint_as_float(qr[4 * ch + 1]) * p.scale,
+                          __uint_as_float(qr[4 * ch + 2]) * p.scale, __uint_as_float(qr[4 * ch + 3]) * p.scale);
         }
       }
+      fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar_free);
+      if (threadIdx.x == 0) BTRACE(14);
     }
     // ---- dK, dV of this key tile (every product has completed: the last bar_dq was waited)
     // (tcgen05.ld is warp-collective: every thread runs the loads, only the
@@ -317,6 +394,19 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     tmem_dealloc(tmem, 512);
   }
 }
+
+#ifdef B200ATTN_TRACE
+}  // namespace
+}  // namespace b200attn
+extern "C" int b200attn_debug_read_bwd_trace(unsigned long long* host_out, int count) {
+  cudaMemcpyFromSymbol(host_out, b200attn::g_bwd_trace, sizeof(unsigned long long) * count);
+  static unsigned long long zeros[5 * b200attn::kBwdTraceSlice];
+  cudaMemcpyToSymbol(b200attn::g_bwd_trace, zeros, sizeof(zeros));
+  return count;
+}
+namespace b200attn {
+namespace {
+#endif
 
 // D[t, h] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head).
 template <typename T>
@@ -392,6 +482,19 @@ bool make_tmap(CUtensorMap* m, int dtype, const void* base, int D, long long tok
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// fp32 [tokens, heads, DP] accumulator as [DP, tokens, heads], box = 32 x 128 x 1, 128B swizzle
+bool make_dq_tmap(CUtensorMap* m, float* base, int DP, long long tokens, int heads) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)DP, (cuuint64_t)tokens, (cuuint64_t)heads};
+  cuuint64_t strides[2] = {(cuuint64_t)heads * DP * 4, (cuuint64_t)DP * 4};
+  cuuint32_t box[3] = {32, (cuuint32_t)kT, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int dpad(int d) { return d <= 64 ? 64 : 128; }
 
 long long total_rows(const b200attn_prefill_bwd_args* a) {
@@ -439,13 +542,11 @@ int launch_bwd(const b200attn_prefill_bwd_args* a, const BwdParams& p, cudaStrea
       !make_tmap(&tdo, a->dtype, a->d_o, a->head_dim, tokens, a->heads_q, tb, a->do_stride_t, a->do_stride_h, a->do_stride_b))
     return B200ATTN_ERR_CUDA;
   auto kern = bwd_kernel<T, DP>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
-      return B200ATTN_ERR_CUDA;
-    attr_set = true;
-  }
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
+    return B200ATTN_ERR_CUDA;
   const long long rows = total_rows(a);
+  CUtensorMap tdq;
+  if (!make_dq_tmap(&tdq, p.dq_acc, DP, rows / a->heads_q, a->heads_q)) return B200ATTN_ERR_CUDA;
   const int tpb = a->cu_seqlens ? (int)a->total_tokens : a->seqlen;   // tokens per batch entry of the dense index
   // 1. D = rowsum(dO o O)
   {
@@ -459,7 +560,7 @@ int launch_bwd(const b200attn_prefill_bwd_args* a, const BwdParams& p, cudaStrea
   // 2. main kernel (dq accumulator zeroed first)
   if (cudaMemsetAsync(p.dq_acc, 0, (size_t)rows * DP * 4, stream) != cudaSuccess) return B200ATTN_ERR_CUDA;
   dim3 grid(p.n_kvtiles, a->heads_kv, a->batch);
-  kern<<<grid, kBwdThreads, L::kAlloc, stream>>>(tq, tk, tv, tdo, p);
+  kern<<<grid, kBwdThreads, L::kAlloc, stream>>>(tq, tk, tv, tdo, tdq, p);
   // 3. dq accumulator -> dq
   {
     const long long items = rows * (DP / 8);
