@@ -16,9 +16,12 @@
 // tcgen05.mma: S and dP with both operands K-major from shared memory; P and
 // dS are written by the softmax threads into 128-byte-swizzled shared memory
 // once and read twice, as the MN-major A operand of dV / dK and as the K-major
-// A operand of dQ.  TMEM columns: S then dQ [0,128), dP [128,256), dK
-// [256,384), dV [384,512).  This first version runs the steps of one (query
-// tile, key tile) pair one after the other (no software pipelining).
+// A operand of dQ.  TMEM columns: S [0,128), dP then dQ [128,256), dK
+// [256,384), dV [384,512).  Pipelining across (query tile, key tile) pairs: the
+// query tiles are double buffered and the next pair's S is issued right behind
+// this pair's dQ; dO is refetched as soon as the dV product has read it (and asked
+// into L2 a pair ahead); the fp32 dQ tile leaves through shared memory and a copy-
+// engine reduce-add, which runs while the next pair is computed.
 #include <type_traits>
 
 #include "common.cuh"
@@ -29,7 +32,11 @@ using namespace sm100;
 
 namespace {
 
-constexpr int kBwdThreads = 160;   // warps 0-3: one thread per row; warp 4: TMA + MMA issue
+constexpr int kBwdComputeWarps = 8;   // warps 0-7: two threads per row (64 columns each)
+constexpr int kBwdCtrlWarp = kBwdComputeWarps;                // MMA issue, Q reloads, dQ reduce-adds
+constexpr int kBwdLoadWarp = kBwdComputeWarps + 1;            // K, V, dO loads
+constexpr int kBwdThreads = 32 * (kBwdComputeWarps + 2);
+constexpr int kBwdComputeThreads = 32 * kBwdComputeWarps;
 constexpr int kT = 128;            // rows / keys per tile
 
 struct BwdParams {
@@ -58,7 +65,7 @@ __device__ __forceinline__ float ex2f(float x) {
 #ifdef B200ATTN_TRACE
 // Debug builds only: (event id, SM clock) of one CTA, one slice per warp.
 constexpr int kBwdTraceSlice = 4096;
-__device__ unsigned long long g_bwd_trace[5 * kBwdTraceSlice];
+__device__ unsigned long long g_bwd_trace[10 * kBwdTraceSlice];
 __device__ __forceinline__ void bwd_trace_ev(int id, unsigned& n) {
   if (blockIdx.x != 0 || blockIdx.y != 3 || blockIdx.z != 1) return;   // a CTA with the longest walk
   long long c;
@@ -82,9 +89,11 @@ struct BwdSmem {
   static constexpr int kK = 0, kV = kOperand, kQ = 2 * kOperand, kDO = 3 * kOperand;
   static constexpr int kP = 4 * kOperand, kDS = kP + kPds;
   static constexpr int kQ1 = kDS + kPds;             // second Q tile (query tiles are double buffered)
-  static constexpr int kStage = kP;                  // fp32 dQ tile on its way to global memory: reuses P, dS
-  static constexpr int kStagePanel = kT * 128;       // 32 fp32 columns of 128 rows, 128-byte swizzle
-  static_assert((DP / 32) * kStagePanel <= 2 * kPds, "dQ staging fits in the P and dS tiles");
+  // The fp32 dQ tile leaves through shared memory in panels of 32 columns (128 rows,
+  // 128-byte swizzle): the first half of the panels in the P tile, the second half in
+  // the pair's own Q buffer, both dead by the time dQ exists.
+  static constexpr int kStagePanel = kT * 128;
+  static_assert((DP / 64) * kStagePanel <= kPds && (DP / 64) * kStagePanel <= kOperand, "dQ staging fits");
   static constexpr int kBarOffset = kQ1 + kOperand;
   static constexpr int kNumBars = 9;
   static constexpr int kBytes = kBarOffset + kNumBars * 8 + 16;
@@ -136,9 +145,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     mbar_init(bar_do, 1);
     mbar_init(bar_dv, 1);
     mbar_init(bar_sdp, 1);
-    mbar_init(bar_pds, kT);
+    mbar_init(bar_pds, kBwdComputeThreads);
     mbar_init(bar_dq, 1);
-    mbar_init(bar_free, kT);
+    mbar_init(bar_free, kBwdComputeThreads);
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -153,18 +162,50 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tDP = tmem + 128, tDK = tmem + 256, tDV = tmem + 384;
 
-  if (warp == 4) {
-    // ============================================ control warp: TMA + MMA issue
-    const uint32_t issue = elect_one() ? 1u : 0u;
-    if (issue) {
+  // query tile and head of pair `it`
+  auto pair_of = [&](int it, int& i, int& hq) { i = i_first + it / p.group; hq = hk * p.group + it % p.group; };
+  if (warp == kBwdLoadWarp) {
+    // ============================================ loader warp: K, V, the first Q tiles, every dO tile
+    // (dO has one buffer: pair it + 1's tile is fetched the moment the dV product of
+    // pair it has read it, which must not wait for the MMA warp to finish issuing)
+    if (elect_one()) {
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
       mbar_expect_tx(bar_kv, 2 * L::kOperand);
       for (int pn = 0; pn < kPanels; ++pn) {
         tma_load_4d(sbase + L::kK + pn * L::kPanel, &tmap_k, bar_kv, 64 * pn, seq_start + kv0, hk, bcoord);
         tma_load_4d(sbase + L::kV + pn * L::kPanel, &tmap_v, bar_kv, 64 * pn, seq_start + kv0, hk, bcoord);
       }
+      for (int it = 0; it < min(n_iter, 2); ++it) {
+        int i, hq;
+        pair_of(it, i, hq);
+        const uint32_t dst = sbase + (it ? L::kQ1 : L::kQ), bar = bar_q0 + 8 * it;
+        mbar_expect_tx(bar, L::kOperand);
+        for (int pn = 0; pn < kPanels; ++pn)
+          tma_load_4d(dst + pn * L::kPanel, &tmap_q, bar, 64 * pn, seq_start + i * kT, hq, bcoord);
+      }
+      for (int it = 0; it < n_iter; ++it) {
+        int i, hq;
+        pair_of(it, i, hq);
+        if (it > 0) mbar_wait(bar_dv, (it - 1) & 1, abort_flag);
+        BTRACE(20);
+        mbar_expect_tx(bar_do, L::kOperand);
+        for (int pn = 0; pn < kPanels; ++pn)
+          tma_load_4d(sbase + L::kDO + pn * L::kPanel, &tmap_do, bar_do, 64 * pn, seq_start + i * kT, hq, bcoord);
+        if (it + 1 < n_iter) {        // next pair's dO, and the Q tile after next, into L2
+          int in, hqn;
+          pair_of(it + 1, in, hqn);
+          for (int pn = 0; pn < kPanels; ++pn) tma_prefetch_4d(&tmap_do, 64 * pn, seq_start + in * kT, hqn, bcoord);
+          if (it + 2 < n_iter) {
+            pair_of(it + 2, in, hqn);
+            for (int pn = 0; pn < kPanels; ++pn) tma_prefetch_4d(&tmap_q, 64 * pn, seq_start + in * kT, hqn, bcoord);
+          }
+        }
+      }
     }
     __syncwarp();
+  } else if (warp == kBwdCtrlWarp) {
+    // ============================================ MMA warp: products, Q reloads, dQ reduce-adds
+    const uint32_t issue = elect_one() ? 1u : 0u;
     const uint64_t d_k = smem_desc_sw128(sbase + L::kK, 16, 1024);
     const uint64_t d_v = smem_desc_sw128(sbase + L::kV, 16, 1024);
     const uint64_t d_do = smem_desc_sw128(sbase + L::kDO, 16, 1024);
@@ -173,57 +214,38 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     const uint64_t d_ds_k = smem_desc_sw128(sbase + L::kDS, 16, 1024);           // same bytes, M = q
     const uint64_t d_do_mn = smem_desc_sw128(sbase + L::kDO, L::kPanel, 1024);   // [q][d] read with K = q
     const uint64_t d_k_mn = smem_desc_sw128(sbase + L::kK, L::kPanel, 1024);     // [k][d] read with K = k
-    // query tile and head of pair `it`
-    auto pair_of = [&](int it, int& i, int& hq) { i = i_first + it / p.group; hq = hk * p.group + it % p.group; };
-    auto load_q = [&](int it) {        // into buffer it & 1
-      int i, hq;
-      pair_of(it, i, hq);
-      const uint32_t dst = sbase + ((it & 1) ? L::kQ1 : L::kQ), bar = bar_q0 + 8 * (it & 1);
-      if (issue) {
-        mbar_expect_tx(bar, L::kOperand);
-        for (int pn = 0; pn < kPanels; ++pn)
-          tma_load_4d(dst + pn * L::kPanel, &tmap_q, bar, 64 * pn, seq_start + i * kT, hq, bcoord);
-      }
-      __syncwarp();
-    };
-    auto load_do = [&](int it) {
-      int i, hq;
-      pair_of(it, i, hq);
-      if (issue) {
-        mbar_expect_tx(bar_do, L::kOperand);
-        for (int pn = 0; pn < kPanels; ++pn)
-          tma_load_4d(sbase + L::kDO + pn * L::kPanel, &tmap_do, bar_do, 64 * pn, seq_start + i * kT, hq, bcoord);
-      }
-      __syncwarp();
-    };
-    if (n_iter > 0) { load_q(0); load_do(0); }
-    for (int it = 0; it < n_iter; ++it) {
-      int i, hq;
-      pair_of(it, i, hq);
-      // The other Q buffer was last read by pair it - 1, whose products are complete
-      // (its dQ tile has been taken out of TMEM): fetch the next query tile now.
-      if (it + 1 < n_iter) load_q(it + 1);
-      const uint32_t q_off = (it & 1) ? L::kQ1 : L::kQ;
-      const uint64_t d_q = smem_desc_sw128(sbase + q_off, 16, 1024);
-      const uint64_t d_q_mn = smem_desc_sw128(sbase + q_off, L::kPanel, 1024);
-      if (it == 0) mbar_wait(bar_kv, 0, abort_flag);
-      mbar_wait(bar_q0 + 8 * (it & 1), (it >> 1) & 1, abort_flag);
-      mbar_wait(bar_do, it & 1, abort_flag);
-      tc_fence_after();
-      if (issue) BTRACE(3);
-      // S = Q K^T, dP = dO V^T
+    auto issue_s = [&](int itx) {      // S = Q K^T of pair itx (its Q buffer must have landed)
+      const uint64_t dq_x = smem_desc_sw128(sbase + ((itx & 1) ? L::kQ1 : L::kQ), 16, 1024);
 #pragma unroll
       for (int ks = 0; ks < DP / 16; ++ks) {
         const uint64_t off = (uint64_t)(((ks / 4) * L::kPanel + (ks % 4) * 32) >> 4);
-        mma_ss(tS, d_q + off, d_k + off, kIdSS, ks > 0, issue);
+        mma_ss(tS, dq_x + off, d_k + off, kIdSS, ks > 0, issue);
       }
+    };
+    for (int it = 0; it < n_iter; ++it) {
+      int i, hq;
+      pair_of(it, i, hq);
+      const uint32_t q_off = (it & 1) ? L::kQ1 : L::kQ;
+      const uint64_t d_q_mn = smem_desc_sw128(sbase + q_off, L::kPanel, 1024);
+      if (it == 0) {
+        mbar_wait(bar_kv, 0, abort_flag);
+        mbar_wait(bar_q0, 0, abort_flag);
+        tc_fence_after();
+        issue_s(0);
+      }
+      // (S of later pairs is issued at the end of the pair before, behind its dQ product)
+      mbar_wait(bar_do, it & 1, abort_flag);
+      tc_fence_after();
+      if (issue) BTRACE(3);
+      // dP = dO V^T
 #pragma unroll
       for (int ks = 0; ks < DP / 16; ++ks) {
         const uint64_t off = (uint64_t)(((ks / 4) * L::kPanel + (ks % 4) * 32) >> 4);
         mma_ss(tDP, d_do + off, d_v + off, kIdSS, ks > 0, issue);
       }
-      // the previous pair's dQ tile must have left the P / dS bytes before they are rewritten
-      if (issue) bulk_wait_read_all();
+      // the first half of the previous pair's dQ tile must have left the P bytes before
+      // they are rewritten (the second half sits in a Q buffer and may still be on its way)
+      if (issue) bulk_wait_read_but_one();
       __syncwarp();
       mma_commit(bar_sdp, issue);
       if (issue) BTRACE(4);
@@ -231,6 +253,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       mbar_wait(bar_pds, it & 1, abort_flag);
       tc_fence_after();
       if (issue) BTRACE(5);
+      // The Q buffer of pair it - 1 held the second half of its dQ tile; once that is
+      // read it takes the query tile of pair it + 1 (in L2 by now).
+      if (it > 0 && it + 1 < n_iter) {
+        int in, hqn;
+        pair_of(it + 1, in, hqn);
+        if (issue) {
+          bulk_wait_read_all();
+          const uint32_t dst = sbase + (((it + 1) & 1) ? L::kQ1 : L::kQ), bar = bar_q0 + 8 * ((it + 1) & 1);
+          mbar_expect_tx(bar, L::kOperand);
+          for (int pn = 0; pn < kPanels; ++pn)
+            tma_load_4d(dst + pn * L::kPanel, &tmap_q, bar, 64 * pn, seq_start + in * kT, hqn, bcoord);
+        }
+        __syncwarp();
+      }
       const uint32_t acc = it > 0 ? 1u : 0u;
 #pragma unroll
       for (int ks = 0; ks < kT / 16; ++ks) {   // contraction over the 128 queries
@@ -247,31 +283,43 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       for (int ks = 0; ks < kT / 16; ++ks) {   // contraction over the 128 keys
         const uint64_t offa = (uint64_t)(((ks / 4) * L::kPanel + (ks % 4) * 32) >> 4);
         const uint64_t offb = (uint64_t)((ks * 2048) >> 4);
-        mma_ss(tS, d_ds_k + offa, d_k_mn + offb, kIdDQ, ks > 0, issue);
+        mma_ss(tDP, d_ds_k + offa, d_k_mn + offb, kIdDQ, ks > 0, issue);   // dQ takes the dP columns
       }
       mma_commit(bar_dq, issue);
       if (issue) BTRACE(6);
-      // dO is last read by the dV product: fetch the next pair's while dK and dQ run
-      mbar_wait(bar_dv, it & 1, abort_flag);
-      if (it + 1 < n_iter) load_do(it + 1);
-      // the compute warps have moved the scaled dQ tile into shared memory: add it to the
-      // fp32 accumulator in global memory (rows past the sequence end hold exact zeros)
+      // the S columns were read before P and dS were written: start the next pair's scores
+      // now, so they are computed while this pair's dQ tile is being moved out
+      if (it + 1 < n_iter) {
+        mbar_wait(bar_q0 + 8 * ((it + 1) & 1), ((it + 1) >> 1) & 1, abort_flag);
+        tc_fence_after();
+        issue_s(it + 1);
+      }
+      // the compute warps have moved the scaled dQ tile into shared memory (first half of
+      // the columns in the P tile, second half in this pair's Q buffer): add both to the
+      // fp32 accumulator in global memory, one bulk group each.  Rows past the sequence
+      // end hold exact zeros.
       mbar_wait(bar_free, it & 1, abort_flag);
       if (issue) BTRACE(2);
       if (issue) {
         const int tl0 = (p.cu_seqlens ? seq_start : b * p.seqlen) + i * kT;
-        for (int pn = 0; pn < DP / 32; ++pn)
-          tma_reduce_add_3d(&tmap_dq, sbase + L::kStage + pn * L::kStagePanel, 32 * pn, tl0, hq);
+        for (int pn = 0; pn < DP / 64; ++pn)
+          tma_reduce_add_3d(&tmap_dq, sbase + L::kP + pn * L::kStagePanel, 32 * pn, tl0, hq);
+        bulk_commit_group();
+        for (int pn = 0; pn < DP / 64; ++pn)
+          tma_reduce_add_3d(&tmap_dq, sbase + q_off + pn * L::kStagePanel, 32 * (DP / 64 + pn), tl0, hq);
         bulk_commit_group();
       }
       __syncwarp();
     }
     if (issue) bulk_wait_all();
     __syncwarp();
-  } else {
-    // ============================================ compute warps: one thread per row
-    const int row = threadIdx.x;                         // query row in the tile / key row in the epilogue
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+  } else if (warp < kBwdComputeWarps) {
+    // ============================================ compute warps: two threads per row
+    // Two threads per row: warps w and w + 4 share TMEM lanes 32 (w % 4) .., each takes half
+    // of the columns, so every scheduler has two warps to switch between.
+    const int row = threadIdx.x & (kT - 1);              // query row in the tile / key row in the epilogue
+    const int half = threadIdx.x >> 7;                   // which half of the columns
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     uint8_t* sP = sgen + L::kP;
     uint8_t* sDS = sgen + L::kDS;
     for (int it = 0; it < n_iter; ++it) {
@@ -296,8 +344,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       // visible keys of this row inside the tile: columns [0, lim)
       int lim = live ? min(kT, len - kv0) : 0;
       if (p.causal) lim = min(lim, qi - kv0 + 1);
+      const bool masked = __any_sync(0xffffffffu, lim < kT);   // only diagonal and ragged tiles
 #pragma unroll
-      for (int cc = 0; cc < kT / 32; ++cc) {
+      for (int c2 = 0; c2 < kT / 64; ++c2) {
+        const int cc = 2 * half + c2;                    // 32-column group
         uint32_t sr[32], dr[32];
         tmem_ld32(tS + lane_off + 32 * cc, sr);
         tmem_ld32(tDP + lane_off + 32 * cc, dr);
@@ -309,9 +359,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
           float p1 = ex2f(fmaf(__uint_as_float(sr[x + 1]), p.scale_log2, -lse2));
           float d0 = p0 * (__uint_as_float(dr[x]) - dsum);
           float d1 = p1 * (__uint_as_float(dr[x + 1]) - dsum);
-          // masked entries are exact zeros whatever S and dP hold there
-          if (32 * cc + x >= lim) { p0 = 0.f; d0 = 0.f; }
-          if (32 * cc + x + 1 >= lim) { p1 = 0.f; d1 = 0.f; }
+          if (masked) {
+            // masked entries are exact zeros whatever S and dP hold there
+            if (32 * cc + x >= lim) { p0 = 0.f; d0 = 0.f; }
+            if (32 * cc + x + 1 >= lim) { p1 = 0.f; d1 = 0.f; }
+          }
           pp[x / 2] = pack2<T>(p0, p1);
           dd[x / 2] = pack2<T>(d0, d1);
         }
@@ -334,15 +386,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       if (threadIdx.x == 0) BTRACE(13);
       // scaled fp32 tile -> shared memory in the copy engine's 128-byte-swizzled layout
       // (one panel per 32 columns); the control warp adds it to global memory
-      uint8_t* sStage = sgen + L::kStage;
+      uint8_t* sStage = sgen + (half == 0 ? L::kP : ((it & 1) ? L::kQ1 : L::kQ));
 #pragma unroll
-      for (int cc = 0; cc < DP / 32; ++cc) {
+      for (int c2 = 0; c2 < DP / 64; ++c2) {
+        const int cc = (DP / 64) * half + c2;
         uint32_t qr[32];
-        tmem_ld32(tS + lane_off + 32 * cc, qr);
+        tmem_ld32(tDP + lane_off + 32 * cc, qr);
         tmem_wait_ld();
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
-          const uint32_t off = cc * L::kStagePanel + row * 128 + ((ch ^ (row & 7)) << 4);
+          const uint32_t off = c2 * L::kStagePanel + row * 128 + ((ch ^ (row & 7)) << 4);
           *reinterpret_cast<float4*>(sStage + off) =
               make_float4(__uint_as_float(qr[4 * ch]) * p.scale, __uint_as_float(qr[4 * ch + 1]) * p.scale,
                           __uint_as_float(qr[4 * ch + 2]) * p.scale, __uint_as_float(qr[4 * ch + 3]) * p.scale);
@@ -366,7 +419,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       const float sc = which ? 1.f : p.scale;
       T* dst = which ? dvrow : dkrow;
 #pragma unroll
-      for (int cc = 0; cc < DP / 32; ++cc) {
+      for (int c2 = 0; c2 < DP / 64; ++c2) {
+        const int cc = (DP / 64) * half + c2;
         uint32_t r[32];
         tmem_ld32((which ? tDV : tDK) + lane_off + 32 * cc, r);
         tmem_wait_ld();
@@ -400,7 +454,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
 }  // namespace b200attn
 extern "C" int b200attn_debug_read_bwd_trace(unsigned long long* host_out, int count) {
   cudaMemcpyFromSymbol(host_out, b200attn::g_bwd_trace, sizeof(unsigned long long) * count);
-  static unsigned long long zeros[5 * b200attn::kBwdTraceSlice];
+  static unsigned long long zeros[10 * b200attn::kBwdTraceSlice];
   cudaMemcpyToSymbol(b200attn::g_bwd_trace, zeros, sizeof(zeros));
   return count;
 }
