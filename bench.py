@@ -31,7 +31,7 @@ sys.path.insert(0, ROOT)
 METRIC = "prefill attn TFLOP/s & decode KV HBM GB/s per B200, at 1/2/4/8 GPUs"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # ncu captures summarised under profiles/ (same workloads as below)
-TRAFFIC = {"cfg2": 402.877184e6 + 120.129792e6, "cfg3": 1.299476e9 + 9.861120e6,
+TRAFFIC = {"cfg2": 402.877184e6 + 120.129792e6, "cfg3": 1.301270e9 + 6.896384e6, "cfg2_backward": 809.810176e6 + 491.803392e6,
            "cfg4": 554.967296e6 + 121.874176e6, "cfg5": 2.148035e9 + 14.810368e6}
 WORKLOAD = "cfg2: dense causal prefill bf16 B=4 H=32 S=4096 D=128 per GPU"
 
@@ -260,7 +260,7 @@ def run_ours(args, rank, world, local_rank):
         other["cfg2_backward"] = {
             "value": tfb * world, "unit": "TFLOP/s", "ms_per_step": msb,
             "roofline": {"bound": "tensor", "achieved": tfb, "peak": pk["tflops"], "unit": "TFLOP/s",
-                         "frac": tfb / pk["tflops"], "traffic": None},
+                         "frac": tfb / pk["tflops"], "traffic": TRAFFIC["cfg2_backward"]},
             "config": {"workload": "backward of cfg2 (dense causal bf16 B=4 H=32 S=4096 D=128): dQ, dK, dV",
                        "flops": "2.5 x the causal forward count (five products instead of two)"}}
         del o2, lse2, do2
@@ -345,6 +345,12 @@ def run_single(args, dev, sync, barrier, pk):
         w = workloads.cfg3(dev)
         fn = lambda: ops.decode(w.q, w.k_cache, w.v_cache, cu_seqlens=w.cu_seqlens, max_seqlen=w.max_seqlen)
         work, unit, peak = w.kv_bytes / 1e6, "GB/s", pk["gbs"]
+    elif args.only == "backward":
+        w = workloads.dense_causal(4, 32, 4096, 128, 1, dev, name="cfg2")
+        o, lse = ops.prefill(w.q, w.k, w.v, cu_seqlens=w.cu_seqlens, max_seqlen=w.max_seqlen)
+        d_o = torch.randn(o.shape, device=dev, dtype=torch.float32).to(o.dtype)
+        fn = lambda: ops.prefill_bwd(w.q, w.k, w.v, o, d_o, lse, cu_seqlens=w.cu_seqlens, max_seqlen=w.max_seqlen)
+        work, unit, peak = 2.5 * w.flops / 1e9, "TFLOP/s", pk["tflops"]
     elif args.only == "sparse_prefill":
         w = workloads.cfg4(dev)
         fn = lambda: ops.prefill(w.q, w.k, w.v, cu_seqlens=w.cu_seqlens, max_seqlen=w.max_seqlen,
@@ -367,7 +373,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="all",
-                    choices=["all", "prefill", "decode", "sparse_prefill", "sparse_decode"],
+                    choices=["all", "prefill", "decode", "backward", "sparse_prefill", "sparse_decode"],
                     help="profiling aid: run one kernel's timed loop and print a short line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
