@@ -213,17 +213,22 @@ def run_ours(args, rank, world, local_rank):
     hl = torch.empty(w.q.shape[:3], dtype=torch.float32).pin_memory()
     dq, dk, dv = (torch.empty_like(t) for t in (w.q, w.k, w.v))
 
+    # the package's host-buffer entry point: per sequence copy in / attend / copy out on three
+    # streams, so the PCIe transfers overlap the kernels and each other (same arithmetic as above)
+    from tritonops_b200.host import HostPrefill
+    pipe = HostPrefill(dev)
+    cu_host = [int(x) for x in w.cu_seqlens.cpu()]
+    del dq, dk, dv
+
     def e2e_step():
-        dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True); dv.copy_(hv, non_blocking=True)
-        o, lse = flash_attn_triton_fwd(dq, dk, dv, w.cu_seqlens, sm_scale, max_seqlen=w.max_seqlen)
-        ho.copy_(o, non_blocking=True); hl.copy_(lse, non_blocking=True)
+        pipe.run(hq, hk, hv, cu_host, ho, hl, scale=sm_scale, scale_has_log2e=True, causal=True, lse_base2=True)
 
     e2e_steps = max(3, min(args.steps, 10))
     ms_e2e = reduce_max(time_steps(e2e_step, e2e_steps, 3, sync, barrier))
     h2d = 3 * w.q.numel() * w.q.element_size() if w.k.shape == w.q.shape else \
         (w.q.numel() + 2 * w.k.numel()) * w.q.element_size()
     d2h = ho.numel() * ho.element_size() + hl.numel() * 4
-    del hq, hk, hv, ho, hl, dq, dk, dv
+    del hq, hk, hv, ho, hl, pipe
 
     other = {}
     # ---------------- config 3: GQA decoding (HBM bound)
@@ -326,7 +331,9 @@ def run_ours(args, rank, world, local_rank):
                      "algorithmic_bytes": 4 * w.q.numel() * 2 + w.q.numel() // 128 * 4},
         "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": total_flops / ms_e2e / 1e9, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "api": "tritonops_b200.host.HostPrefill.run(pinned q, k, v -> pinned o, lse2), one sequence per "
+                       "copy-in / kernel / copy-out stage on three streams"},
         "gpu_launches": launches,
         "clocks": clocks,
         "other": other,
