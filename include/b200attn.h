@@ -40,7 +40,7 @@ typedef enum {
   B200ATTN_ERR_DEVICE = -12      /* current device is not compute capability 10.x */
 } b200attn_status;
 
-typedef enum { B200ATTN_F16 = 0, B200ATTN_BF16 = 1 } b200attn_dtype;
+typedef enum { B200ATTN_F16 = 0, B200ATTN_BF16 = 1, B200ATTN_F32 = 2 /* RMSNorm only */ } b200attn_dtype;
 
 typedef enum {
   B200ATTN_DENSE = 0,       /* every (causally) visible key */
@@ -364,6 +364,51 @@ typedef struct {
  * reference, whose tests rebuild the whole cache instead
  * (flash_attn_triton/flash_attn_decoding_sparse.py:445-466). */
 int b200attn_kv_append(const b200attn_kv_append_args* args, b200attn_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * RMSNorm over the last dimension of a [rows, dim] view (the op in front of the
+ * QKV projection).  x / y / dy / dx share one dtype (F16, BF16 or F32); weight
+ * and dweight have that dtype or F32.  Row strides are in elements, the inner
+ * stride is 1.  Arithmetic is fp32.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const void* x;
+  const void* weight;          /* [dim] */
+  void* y;
+  float* rstd;                 /* nullable; fp32 [rows] = (mean(x^2) + eps)^-1/2, needed by the backward */
+  int32_t x_dtype, w_dtype;
+  int64_t rows;
+  int32_t dim;
+  int64_t x_stride_row, y_stride_row;
+  float eps;
+} b200attn_rmsnorm_fwd_args;
+
+/* y = x * rstd * weight.  Replaces RMSNormTritonFunction.forward and
+ * rmsnorm_fwd_kernel (common/rms.py:221-290, :9-88). */
+int b200attn_rmsnorm_fwd(const b200attn_rmsnorm_fwd_args* args, b200attn_stream_t stream);
+
+typedef struct {
+  const void* dy;
+  const void* x;
+  const void* weight;
+  const float* rstd;           /* from the forward */
+  void* dx;
+  void* dweight;               /* [dim], overwritten */
+  int32_t x_dtype, w_dtype;
+  int64_t rows;
+  int32_t dim;                 /* <= 16384 */
+  int64_t dy_stride_row, x_stride_row, dx_stride_row;
+  void* workspace;             /* fp32 partial sums of dweight */
+  size_t workspace_bytes;
+} b200attn_rmsnorm_bwd_args;
+
+size_t b200attn_rmsnorm_bwd_workspace_bytes(const b200attn_rmsnorm_bwd_args* args);
+
+/* dx and dweight.  Replaces RMSNormTritonFunction.backward and rmsnorm_bwd_kernel
+ * (common/rms.py:292-355, :91-218); dweight is summed in a fixed order instead of
+ * with atomics (:217), and the weights used inside the row sum are those of the
+ * summed columns (the reference kernel takes another block's for dim > 128, :197-199). */
+int b200attn_rmsnorm_bwd(const b200attn_rmsnorm_bwd_args* args, b200attn_stream_t stream);
 
 /* Prefill needs no scratch; kept so callers can size buffers uniformly. */
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args* args);

@@ -175,7 +175,8 @@ def test_struct_sizes_of_selection_and_paged_args(lib):
              ("b200attn_window_blocks_prefill_args", _lib.WindowBlocksPrefillArgs),
              ("b200attn_window_blocks_decode_args", _lib.WindowBlocksDecodeArgs),
              ("b200attn_topk_blocks_args", _lib.TopkBlocksArgs),
-             ("b200attn_kv_pack_args", _lib.KvPackArgs), ("b200attn_kv_append_args", _lib.KvAppendArgs)]
+             ("b200attn_kv_pack_args", _lib.KvPackArgs), ("b200attn_kv_append_args", _lib.KvAppendArgs),
+             ("b200attn_rmsnorm_fwd_args", _lib.RmsNormFwdArgs), ("b200attn_rmsnorm_bwd_args", _lib.RmsNormBwdArgs)]
     with tempfile.TemporaryDirectory() as d:
         src = os.path.join(d, "p.c")
         body = "".join(f'printf("%zu\\n", sizeof({n}));' for n, _ in names)
@@ -210,4 +211,7 @@ def test_new_entry_points_validate_before_touching_the_device(lib):
     assert L.b200attn_window_blocks_decode(C.byref(c), None) == -1
     d = _lib.PagedDecodeArgs()
     assert L.b200attn_paged_decode_fwd(C.byref(d), None) == -1
+    assert L.b200attn_rmsnorm_fwd(C.byref(_lib.RmsNormFwdArgs()), None) == -1
+    assert L.b200attn_rmsnorm_bwd(C.byref(_lib.RmsNormBwdArgs()), None) == -1
+    assert L.b200attn_rmsnorm_bwd_workspace_bytes(C.byref(_lib.RmsNormBwdArgs(rows=1000, dim=4096))) == 592 * 4096 * 4
     assert L.b200attn_paged_decode_workspace_bytes(C.byref(d)) == 0

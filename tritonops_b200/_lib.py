@@ -8,7 +8,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "csrc", "libb200attn.so")
 
-F16, BF16 = 0, 1
+F16, BF16, F32 = 0, 1, 2
 DENSE, WINDOW, BLOCK_LIST = 0, 1, 2
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
@@ -109,6 +109,19 @@ class TopkBlocksArgs(C.Structure):
                 ("block_idx", vp), ("block_cnt", vp)]
 
 
+class RmsNormFwdArgs(C.Structure):
+    _fields_ = [("x", vp), ("weight", vp), ("y", vp), ("rstd", vp),
+                ("x_dtype", i32), ("w_dtype", i32), ("rows", i64), ("dim", i32),
+                ("x_stride_row", i64), ("y_stride_row", i64), ("eps", f32)]
+
+
+class RmsNormBwdArgs(C.Structure):
+    _fields_ = [("dy", vp), ("x", vp), ("weight", vp), ("rstd", vp), ("dx", vp), ("dweight", vp),
+                ("x_dtype", i32), ("w_dtype", i32), ("rows", i64), ("dim", i32),
+                ("dy_stride_row", i64), ("x_stride_row", i64), ("dx_stride_row", i64),
+                ("workspace", vp), ("workspace_bytes", C.c_size_t)]
+
+
 # every symbol include/b200attn.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "b200attn_abi_version": (C.c_int, []),
@@ -131,6 +144,9 @@ SYMBOLS = {
     "b200attn_window_blocks_prefill": (C.c_int, [C.POINTER(WindowBlocksPrefillArgs), vp]),
     "b200attn_window_blocks_decode": (C.c_int, [C.POINTER(WindowBlocksDecodeArgs), vp]),
     "b200attn_topk_blocks": (C.c_int, [C.POINTER(TopkBlocksArgs), vp]),
+    "b200attn_rmsnorm_fwd": (C.c_int, [C.POINTER(RmsNormFwdArgs), vp]),
+    "b200attn_rmsnorm_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(RmsNormBwdArgs)]),
+    "b200attn_rmsnorm_bwd": (C.c_int, [C.POINTER(RmsNormBwdArgs), vp]),
 }
 NOALLOC_SCRATCH_BYTES = 32 << 20
 

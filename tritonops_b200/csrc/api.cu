@@ -101,6 +101,20 @@ int b200attn_topk_blocks(const b200attn_topk_blocks_args* args, b200attn_stream_
   return topk_blocks(args, (cudaStream_t)stream);
 }
 
+int b200attn_rmsnorm_fwd(const b200attn_rmsnorm_fwd_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return rmsnorm_fwd(args, (cudaStream_t)stream);
+}
+
+size_t b200attn_rmsnorm_bwd_workspace_bytes(const b200attn_rmsnorm_bwd_args* args) {
+  return rmsnorm_bwd_workspace_bytes(args);
+}
+
+int b200attn_rmsnorm_bwd(const b200attn_rmsnorm_bwd_args* args, b200attn_stream_t stream) {
+  set_launch_count(0);
+  return rmsnorm_bwd(args, (cudaStream_t)stream);
+}
+
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args*) { return 0; }
 
 int b200attn_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream) {

@@ -12,8 +12,8 @@ from torch import Tensor
 
 from . import _lib
 from ._lib import (BLOCK_LIST, DENSE, WINDOW, DecodeArgs, KvAppendArgs, KvPackArgs, PagedDecodeArgs,
-                   PrefillArgs, PrefillBwdArgs, TopkBlocksArgs, WindowBlocksDecodeArgs,
-                   WindowBlocksPrefillArgs)
+                   PrefillArgs, PrefillBwdArgs, RmsNormBwdArgs, RmsNormFwdArgs, TopkBlocksArgs,
+                   WindowBlocksDecodeArgs, WindowBlocksPrefillArgs)
 
 LOG2E = 1.4426950408889634
 _DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
@@ -411,3 +411,62 @@ def append_kv(k_cache: Tensor, v_cache: Tensor, new_k: Tensor, new_v: Tensor, se
     with torch.cuda.device(k_cache.device):
         _lib.check(_lib.lib().b200attn_kv_append(C.byref(a), _stream(k_cache)))
     _count()
+
+
+# --------------------------------------------------------------------------
+# RMSNorm
+# --------------------------------------------------------------------------
+_DT_RMS = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+
+
+def _rows_view(t: Tensor) -> Tensor:
+    """[..., D] -> [rows, D] with unit inner stride (copies only if it has to)."""
+    t2 = t.reshape(-1, t.shape[-1])
+    return t2 if t2.stride(-1) == 1 else t2.contiguous()
+
+
+def _rms_dtypes(x: Tensor, weight: Tensor):
+    if x.dtype not in _DT_RMS or (weight.dtype != x.dtype and weight.dtype != torch.float32):
+        raise ValueError("b200attn: rmsnorm takes float16 / bfloat16 / float32 rows and weights of that dtype or float32")
+    return _DT_RMS[x.dtype], _DT_RMS[weight.dtype]
+
+
+def rmsnorm_fwd(x: Tensor, weight: Tensor, eps: float) -> Tuple[Tensor, Tensor]:
+    """(y like x, rstd fp32 [rows]); see b200attn_rmsnorm_fwd in include/b200attn.h."""
+    _need_cuda(x, weight)
+    xd, wd = _rms_dtypes(x, weight)
+    x2, w = _rows_view(x), weight.contiguous()
+    if w.numel() != x2.shape[1]:
+        raise ValueError(f"b200attn: expected weight dim {x2.shape[1]}, got {w.numel()}")
+    y = torch.empty_like(x2, memory_format=torch.contiguous_format)
+    rstd = torch.empty(x2.shape[0], device=x.device, dtype=torch.float32)
+    if x2.shape[0] == 0:
+        return y.view(x.shape), rstd
+    a = RmsNormFwdArgs(_ptr(x2), _ptr(w), _ptr(y), _ptr(rstd), xd, wd, x2.shape[0], x2.shape[1],
+                       x2.stride(0), y.stride(0), float(eps))
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().b200attn_rmsnorm_fwd(C.byref(a), _stream(x)))
+    _count()
+    return y.view(x.shape), rstd
+
+
+def rmsnorm_bwd(dy: Tensor, x: Tensor, weight: Tensor, rstd: Tensor) -> Tuple[Tensor, Tensor]:
+    """(dx like x, dweight like weight); see b200attn_rmsnorm_bwd in include/b200attn.h."""
+    _need_cuda(dy, x, weight, rstd)
+    xd, wd = _rms_dtypes(x, weight)
+    if dy.dtype != x.dtype:
+        dy = dy.to(x.dtype)
+    x2, g2, w = _rows_view(x), _rows_view(dy), weight.contiguous()
+    dx = torch.empty_like(x2, memory_format=torch.contiguous_format)
+    dw = torch.empty_like(w)
+    if x2.shape[0] == 0:
+        return dx.view(x.shape), dw.zero_()
+    a = RmsNormBwdArgs(_ptr(g2), _ptr(x2), _ptr(w), _ptr(rstd), _ptr(dx), _ptr(dw), xd, wd, x2.shape[0],
+                       x2.shape[1], g2.stride(0), x2.stride(0), dx.stride(0), None, 0)
+    L = _lib.lib()
+    ws = torch.empty(max(L.b200attn_rmsnorm_bwd_workspace_bytes(C.byref(a)), 16), device=x.device, dtype=torch.uint8)
+    a.workspace, a.workspace_bytes = _ptr(ws), ws.numel()
+    with torch.cuda.device(x.device):
+        _lib.check(L.b200attn_rmsnorm_bwd(C.byref(a), _stream(x)))
+    _count()
+    return dx.view(x.shape), dw
