@@ -410,6 +410,17 @@ size_t b200attn_rmsnorm_bwd_workspace_bytes(const b200attn_rmsnorm_bwd_args* arg
  * summed columns (the reference kernel takes another block's for dim > 128, :197-199). */
 int b200attn_rmsnorm_bwd(const b200attn_rmsnorm_bwd_args* args, b200attn_stream_t stream);
 
+/* Self-test of the bounded device-side wait the kernels use (every spin on an
+ * mbarrier has a cycle budget; when it runs out the CTA raises an abort flag, all
+ * its roles drain, the kernel returns normally and *status_word is set non-zero).
+ * Launches one CTA that waits on a barrier nothing ever completes, with the given
+ * budget in SM cycles (at most 1e8, about 50 ms).  Afterwards *status_word == 3 (the
+ * waiting thread gave up, and a second thread's wait returned at once) and
+ * *waited_cycles (nullable) holds how long the first wait lasted.  The reference has
+ * no counterpart (Triton kernels do not wait on one another). */
+int b200attn_selftest_bounded_wait(int32_t* status_word, int64_t budget_cycles, int64_t* waited_cycles,
+                                   b200attn_stream_t stream);
+
 /* Prefill needs no scratch; kept so callers can size buffers uniformly. */
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args* args);
 

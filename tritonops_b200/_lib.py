@@ -144,6 +144,7 @@ SYMBOLS = {
     "b200attn_window_blocks_prefill": (C.c_int, [C.POINTER(WindowBlocksPrefillArgs), vp]),
     "b200attn_window_blocks_decode": (C.c_int, [C.POINTER(WindowBlocksDecodeArgs), vp]),
     "b200attn_topk_blocks": (C.c_int, [C.POINTER(TopkBlocksArgs), vp]),
+    "b200attn_selftest_bounded_wait": (C.c_int, [vp, i64, vp, vp]),
     "b200attn_rmsnorm_fwd": (C.c_int, [C.POINTER(RmsNormFwdArgs), vp]),
     "b200attn_rmsnorm_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(RmsNormBwdArgs)]),
     "b200attn_rmsnorm_bwd": (C.c_int, [C.POINTER(RmsNormBwdArgs), vp]),

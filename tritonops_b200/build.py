@@ -8,7 +8,7 @@ import sys
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB = os.path.join(CSRC, "libb200attn.so")
-SOURCES = ["api.cu", "decode.cu", "prefill.cu", "prefill_bwd.cu", "kvcache.cu", "blocksel.cu", "rmsnorm.cu"]
+SOURCES = ["api.cu", "decode.cu", "prefill.cu", "prefill_bwd.cu", "kvcache.cu", "blocksel.cu", "rmsnorm.cu", "selftest.cu"]
 HEADERS = ["common.cuh", os.path.join("..", "..", "include", "b200attn.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]

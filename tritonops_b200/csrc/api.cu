@@ -115,6 +115,12 @@ int b200attn_rmsnorm_bwd(const b200attn_rmsnorm_bwd_args* args, b200attn_stream_
   return rmsnorm_bwd(args, (cudaStream_t)stream);
 }
 
+int b200attn_selftest_bounded_wait(int32_t* status_word, int64_t budget_cycles, int64_t* waited_cycles,
+                                   b200attn_stream_t stream) {
+  set_launch_count(0);
+  return selftest_bounded_wait(status_word, (long long)budget_cycles, (long long*)waited_cycles, (cudaStream_t)stream);
+}
+
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args*) { return 0; }
 
 int b200attn_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream) {

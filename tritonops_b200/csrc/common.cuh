@@ -29,6 +29,7 @@ int32_t window_blocks_prefill_max_nnz(int32_t block_size, int32_t window_local, 
 int window_blocks_prefill(const b200attn_window_blocks_prefill_args* a, cudaStream_t stream);
 int window_blocks_decode(const b200attn_window_blocks_decode_args* a, cudaStream_t stream);
 int topk_blocks(const b200attn_topk_blocks_args* a, cudaStream_t stream);
+int selftest_bounded_wait(int32_t* status_word, long long budget_cycles, long long* waited_cycles, cudaStream_t stream);
 int rmsnorm_fwd(const b200attn_rmsnorm_fwd_args* a, cudaStream_t stream);
 size_t rmsnorm_bwd_workspace_bytes(const b200attn_rmsnorm_bwd_args* a);
 int rmsnorm_bwd(const b200attn_rmsnorm_bwd_args* a, cudaStream_t stream);

@@ -59,7 +59,8 @@ constexpr long long kWaitBudgetCycles = 4000000000LL;
 
 // Bounded wait.  `abort_flag` lives in shared memory: once any role gave up,
 // every later wait in the CTA returns at once so all roles drain and exit.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                              long long budget_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
   const long long t0 = clock64();
@@ -67,13 +68,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 255) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
+      if (clock64() - t0 > budget_cycles) {
         *abort_flag = 1;
         return false;
       }
     }
   }
   return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_for(bar, parity, abort_flag, kWaitBudgetCycles);
 }
 
 // ----------------------------------------------------------------------- TMA

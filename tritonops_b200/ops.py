@@ -5,6 +5,7 @@ streams here; all arithmetic runs in libb200attn.so.  No CPU or eager fallback
 exists: CPU tensors are rejected."""
 import ctypes as C
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -20,6 +21,43 @@ _DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
 
 # kernels launched through this module since import (bench accounting)
 launch_counter = 0
+
+
+# Debug mode (B200ATTN_DEBUG_STATUS=1): the prefill kernels get a status word and every call is
+# followed by a stream synchronisation and a check of it, so a bounded device-side wait that gave
+# up surfaces as an exception at the call that caused it.  Off by default (it costs a host sync).
+DEBUG_STATUS = os.environ.get("B200ATTN_DEBUG_STATUS", "0") == "1"
+_status_words = {}
+
+
+def _status_word(dev) -> Tensor:
+    key = torch.device(dev).index
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, device=dev, dtype=torch.int32)
+    return _status_words[key]
+
+
+def _check_status(dev, what: str):
+    if not DEBUG_STATUS:
+        return
+    w = _status_word(dev)
+    torch.cuda.current_stream(dev).synchronize()
+    if int(w.item()) != 0:
+        w.zero_()
+        raise RuntimeError(f"b200attn: a bounded device-side wait gave up inside {what}; its results are invalid")
+
+
+def selftest_bounded_wait(budget_cycles: int = 2_000_000, device="cuda") -> Tuple[int, int]:
+    """Run the library's wait-that-nothing-completes probe: (status word, cycles waited)."""
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError("b200attn ops take CUDA tensors only (there is no CPU path)")
+    st = torch.zeros(1, device=dev, dtype=torch.int32)
+    waited = torch.zeros(1, device=dev, dtype=torch.int64)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().b200attn_selftest_bounded_wait(_ptr(st), int(budget_cycles), _ptr(waited), _stream(st)))
+    _count()
+    return int(st.item()), int(waited.item())
 
 
 def _count():
@@ -265,10 +303,13 @@ def _prefill_op(q: Tensor, k: Tensor, v: Tensor, cu_seqlens: Optional[Tensor], m
     if block_idx is not None:
         a.block_idx, a.block_cnt, a.block_size = _ptr(block_idx), _ptr(block_cnt), block_size
         a.n_qblocks, a.max_nnz = block_idx.shape[2], block_idx.shape[3]
+    if DEBUG_STATUS:
+        a.status_word = _ptr(_status_word(q.device))
     L = _lib.lib()
     fn = L.b200attn_prefill_fwd if sparsity == DENSE else L.b200attn_sparse_prefill_fwd
     with torch.cuda.device(q.device):
         _lib.check(fn(C.byref(a), _stream(q)))
+        _check_status(q.device, "the prefill forward")
     _count()
     return o, lse
 
@@ -341,7 +382,10 @@ def _prefill_bwd_op(q: Tensor, k: Tensor, v: Tensor, o: Tensor, d_o: Tensor, lse
     ws = torch.empty(max(need, 16), device=q.device, dtype=torch.uint8)
     a.workspace, a.workspace_bytes = _ptr(ws), ws.numel()
     with torch.cuda.device(q.device):
+        if DEBUG_STATUS:
+            a.status_word = _ptr(_status_word(q.device))
         _lib.check(L.b200attn_prefill_bwd(C.byref(a), _stream(q)))
+        _check_status(q.device, "the prefill backward")
     _count()
     return dq, dk, dv
 
