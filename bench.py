@@ -31,7 +31,7 @@ sys.path.insert(0, ROOT)
 METRIC = "prefill attn TFLOP/s & decode KV HBM GB/s per B200, at 1/2/4/8 GPUs"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # ncu captures summarised under profiles/ (same workloads as below)
-TRAFFIC = {"cfg2": 402.877184e6 + 120.129792e6, "cfg3": 1.301270e9 + 6.896384e6, "cfg2_backward": 809.810176e6 + 491.803392e6,
+TRAFFIC = {"cfg2": 409.803520e6 + 120.196096e6, "cfg3": 1.301270e9 + 6.896384e6, "cfg2_backward": 809.810176e6 + 491.803392e6,
            "cfg4": 554.967296e6 + 121.874176e6, "cfg5": 2.148035e9 + 14.810368e6}
 WORKLOAD = "cfg2: dense causal prefill bf16 B=4 H=32 S=4096 D=128 per GPU"
 
