@@ -307,6 +307,35 @@ def run_ours(args, rank, world, local_rank):
         del w5
     except Exception as e:
         other["cfg5_block_sparse_decode"] = {"error": repr(e)}
+    # ---------------- config 1: the reference's own small case (latency bound), in microseconds
+    try:
+        w1 = workloads.cfg1(dev)
+        f1 = lambda: ops.prefill(w1.q, w1.k, w1.v, cu_seqlens=w1.cu_seqlens, max_seqlen=w1.max_seqlen,
+                                 causal=False, scale=w1.scale)
+        us_call = reduce_max(time_steps(f1, 200, 20, sync, barrier)) * 1e3      # call rate incl. the Python host path
+        graph_us = None
+        try:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                f1()
+                g1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g1, stream=side):
+                    for _ in range(20):
+                        f1()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            graph_us = reduce_max(time_steps(g1.replay, 50, 5, sync, barrier)) * 1e3 / 20
+            del g1
+        except Exception:
+            graph_us = None
+        other["cfg1_small_noncausal"] = {
+            "value": graph_us if graph_us is not None else us_call, "unit": "us per call",
+            "per_call_with_python_host_path_us": us_call, "per_launch_replayed_from_a_cuda_graph_us": graph_us,
+            "config": {"workload": "cfg1: non-causal fp16 B=1 H=2 S=128 D=64 (8.4 MFLOP, 128 KiB): launch-latency "
+                                   "bound, one CTA"}}
+        del w1
+    except Exception as e:
+        other["cfg1_small_noncausal"] = {"error": repr(e)}
     clocks = sampler.stop()          # sampled over every timed region above
     torch.cuda.empty_cache()
 

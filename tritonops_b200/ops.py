@@ -102,8 +102,7 @@ def decode_workspace_bytes(batch, heads_q, head_dim, max_visible, chunk=0) -> in
     return _lib.lib().b200attn_decode_workspace_bytes(C.byref(a))
 
 
-@torch.library.custom_op("b200attn::decode_fwd", mutates_args=())
-def _decode_op(q: Tensor, k: Tensor, v: Tensor, lens: Tensor, lens_are_cu: bool, max_seqlen: int,
+def _decode_op_impl(q: Tensor, k: Tensor, v: Tensor, lens: Tensor, lens_are_cu: bool, max_seqlen: int,
                scale: float, chunk: int, sparsity: int, window_global: int, window_local: int,
                block_idx: Optional[Tensor], block_cnt: Optional[Tensor],
                block_size: int) -> Tensor:
@@ -142,6 +141,9 @@ def _decode_op(q: Tensor, k: Tensor, v: Tensor, lens: Tensor, lens_are_cu: bool,
     return o
 
 
+_decode_op = torch.library.custom_op("b200attn::decode_fwd", _decode_op_impl, mutates_args=())
+
+
 @_decode_op.register_fake
 def _(q, k, v, lens, lens_are_cu, max_seqlen, scale, chunk, sparsity, window_global,
       window_local, block_idx, block_cnt, block_size):
@@ -159,7 +161,8 @@ def decode(q, k_cache, v_cache, *, cu_seqlens=None, seqlens=None, max_seqlen=Non
         scale = q.shape[-1] ** -0.5
     if max_seqlen is None:
         max_seqlen = k_cache.shape[1]
-    return _decode_op(q, k_cache, v_cache, lens, cu_seqlens is not None, int(max_seqlen),
+    fn = _decode_op if torch.compiler.is_compiling() else _decode_op_impl   # eager: skip the dispatcher
+    return fn(q, k_cache, v_cache, lens, cu_seqlens is not None, int(max_seqlen),
                       float(scale), int(chunk), int(sparsity), int(window_global),
                       int(window_local), _i32(block_idx, q.device), _i32(block_cnt, q.device),
                       int(block_size))
@@ -269,8 +272,7 @@ def topk_blocks(scores: Tensor, top_k: int, *, n_valid: Optional[Tensor] = None,
 # --------------------------------------------------------------------------
 # prefill
 # --------------------------------------------------------------------------
-@torch.library.custom_op("b200attn::prefill_fwd", mutates_args=())
-def _prefill_op(q: Tensor, k: Tensor, v: Tensor, cu_seqlens: Optional[Tensor], max_seqlen: int,
+def _prefill_op_impl(q: Tensor, k: Tensor, v: Tensor, cu_seqlens: Optional[Tensor], max_seqlen: int,
                 scale: float, scale_has_log2e: bool, causal: bool, lse_base2: bool, sparsity: int,
                 window_local: int, window_global: int, block_idx: Optional[Tensor],
                 block_cnt: Optional[Tensor], block_size: int) -> Tuple[Tensor, Tensor]:
@@ -314,6 +316,9 @@ def _prefill_op(q: Tensor, k: Tensor, v: Tensor, cu_seqlens: Optional[Tensor], m
     return o, lse
 
 
+_prefill_op = torch.library.custom_op("b200attn::prefill_fwd", _prefill_op_impl, mutates_args=())
+
+
 @_prefill_op.register_fake
 def _(q, k, v, cu_seqlens, max_seqlen, scale, scale_has_log2e, causal, lse_base2, sparsity,
       window_local, window_global, block_idx, block_cnt, block_size):
@@ -337,7 +342,8 @@ def prefill(q, k, v, *, cu_seqlens=None, max_seqlen=None, scale=None, scale_has_
             max_seqlen = int((cu[1:] - cu[:-1]).max().item()) if cu.numel() > 1 else 0
         else:
             max_seqlen = q.shape[1]
-    return _prefill_op(q, k, v, cu, int(max_seqlen), float(scale), bool(scale_has_log2e),
+    fn = _prefill_op if torch.compiler.is_compiling() else _prefill_op_impl   # eager: skip the dispatcher
+    return fn(q, k, v, cu, int(max_seqlen), float(scale), bool(scale_has_log2e),
                        bool(causal), bool(lse_base2), int(sparsity), int(window_local),
                        int(window_global), _i32(block_idx, q.device), _i32(block_cnt, q.device),
                        int(block_size))
@@ -346,8 +352,7 @@ def prefill(q, k, v, *, cu_seqlens=None, max_seqlen=None, scale=None, scale_has_
 # --------------------------------------------------------------------------
 # prefill backward
 # --------------------------------------------------------------------------
-@torch.library.custom_op("b200attn::prefill_bwd", mutates_args=())
-def _prefill_bwd_op(q: Tensor, k: Tensor, v: Tensor, o: Tensor, d_o: Tensor, lse: Tensor,
+def _prefill_bwd_op_impl(q: Tensor, k: Tensor, v: Tensor, o: Tensor, d_o: Tensor, lse: Tensor,
                     cu_seqlens: Optional[Tensor], max_seqlen: int, scale: float,
                     scale_has_log2e: bool, causal: bool, lse_base2: bool) -> Tuple[Tensor, Tensor, Tensor]:
     _need_cuda(q, k, v, o, d_o, lse, cu_seqlens)
@@ -390,6 +395,9 @@ def _prefill_bwd_op(q: Tensor, k: Tensor, v: Tensor, o: Tensor, d_o: Tensor, lse
     return dq, dk, dv
 
 
+_prefill_bwd_op = torch.library.custom_op("b200attn::prefill_bwd", _prefill_bwd_op_impl, mutates_args=())
+
+
 @_prefill_bwd_op.register_fake
 def _(q, k, v, o, d_o, lse, cu_seqlens, max_seqlen, scale, scale_has_log2e, causal, lse_base2):
     return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
@@ -407,7 +415,8 @@ def prefill_bwd(q, k, v, o, d_o, lse, *, cu_seqlens=None, max_seqlen=None, scale
             max_seqlen = int((cu[1:] - cu[:-1]).max().item()) if cu.numel() > 1 else 0
         else:
             max_seqlen = q.shape[1]
-    return _prefill_bwd_op(q, k, v, o, d_o, lse, cu, int(max_seqlen), float(scale),
+    fn = _prefill_bwd_op if torch.compiler.is_compiling() else _prefill_bwd_op_impl
+    return fn(q, k, v, o, d_o, lse, cu, int(max_seqlen), float(scale),
                            bool(scale_has_log2e), bool(causal), bool(lse_base2))
 
 
