@@ -43,7 +43,10 @@ static_assert(128 * (kLaunchRegs - kOtherRegs) >= 256 * (kSoftmaxRegs - kLaunchR
 constexpr int kTileM = 128;            // query rows per tile
 constexpr int kPairM = 2 * kTileM;     // query rows per CTA
 constexpr float kLazyRescaleLog2 = 8.f;
-constexpr int kHeadGroup = 8;          // (sequence, head) pairs scheduled together
+#ifndef B200ATTN_HEAD_GROUP
+#define B200ATTN_HEAD_GROUP 8
+#endif
+constexpr int kHeadGroup = B200ATTN_HEAD_GROUP;   // (sequence, head) pairs scheduled together
 
 struct PrefillParams {
   void* o;
@@ -383,7 +386,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       // spends ~2.5 us before its first product can start.  Issued behind this CTA's own
       // first loads (in front of them it delayed them: 1041 instead of 1086 TFLOP/s).
       auto prefetch_next_cta = [&]() {
-        if (!blk && p.prefetch_ahead > 0 && blockIdx.x + p.prefetch_ahead < gridDim.x && elect_one()) {
+        if (p.prefetch_ahead > 0 && blockIdx.x + p.prefetch_ahead < gridDim.x && elect_one()) {
           const int bi = blockIdx.x + p.prefetch_ahead;
           const int grp2 = bi / per_group, in2 = bi - grp2 * per_group;
           const int gh2 = min(kHeadGroup, n_bh - grp2 * kHeadGroup);
@@ -398,7 +401,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             for (int pn = 0; pn < kPanels; ++pn) {
               tma_prefetch_4d(&tmap_q, 64 * pn, ss2 + q02, h2, bc2);
               if (q02 + kTileM < len2) tma_prefetch_4d(&tmap_q, 64 * pn, ss2 + q02 + kTileM, h2, bc2);
-              if (seq2.n > 0) {
+              if (!blk && seq2.n > 0) {   // (block lists: the first K / V blocks are not known here)
                 tma_prefetch_4d(&tmap_k, 64 * pn, ss2 + seq2.kv(0) * BN, h2 / p.group, bc2);
                 tma_prefetch_4d(&tmap_v, 64 * pn, ss2 + seq2.kv(0) * BN, h2 / p.group, bc2);
               }
@@ -445,6 +448,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (ns0 > 0) load_blk(&tmap_k, 0, 0);
         if (ns1 > 0) load_blk(&tmap_k, 1, 0);
         for (int j = 0; j < n_steps; ++j) {
+          if (j == 1 || (j == 0 && n_steps == 1)) prefetch_next_cta();
           if (j < ns0) load_blk(&tmap_v, 0, j);
           if (j + 1 < ns0) load_blk(&tmap_k, 0, j + 1);
           if (j < ns1) load_blk(&tmap_v, 1, j);
