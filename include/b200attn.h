@@ -127,7 +127,7 @@ typedef struct {
   int64_t v_stride_b, v_stride_t, v_stride_h;
   int64_t o_stride_b, o_stride_h;
   float softmax_scale;        /* natural scale, e.g. head_dim^-0.5 */
-  int32_t chunk_tokens;       /* split size, multiple of 64; 0 = chosen from the problem size (128..2048) */
+  int32_t chunk_tokens;       /* split size, multiple of 64; 0 = chosen from the problem size (128..8192) */
   /* sparsity (ignored by b200attn_decode_fwd) */
   int32_t sparsity;
   int32_t window_global;      /* WINDOW: key j visible iff j < window_global ... */

@@ -85,6 +85,19 @@ def test_seqlens_form_scale_and_chunk():
     assert maxabs(outs[0], outs[3]) <= 2e-2
 
 
+def test_long_sequences_with_long_chunks():
+    """Few sequences, many keys: the library picks chunks of up to 8192 keys; every explicit
+    chunk size gives the same answer as fp32 math."""
+    ops, _, _, _ = _mods()
+    lens = [20000, 8193]
+    q, kc, vc, cu = make(2, 8, 2, 128, lens, torch.bfloat16, seed=9, tmax=20000)
+    ref = orc.decoding_exact(q, kc, vc, lens)
+    sl = torch.tensor(lens, dtype=torch.int32).cuda()
+    for c in (0, 2048, 4096, 8192):
+        o = ops.decode(q.cuda(), kc.cuda(), vc.cuda(), seqlens=sl, chunk=c)
+        assert maxabs(o, ref) <= 2e-2, c
+
+
 def test_strided_cache_views():
     """Arbitrary batch/token/head strides are honoured (the reference passes all
     strides through, flash_attn_decoding.py:280-297)."""

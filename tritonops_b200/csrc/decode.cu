@@ -619,18 +619,25 @@ static int decode_max_visible(const b200attn_decode_args* a) {
   return a->max_seqlen;
 }
 
-// Split size.  Longer chunks amortise a CTA's pipeline fill and combine (config 3:
-// 5.5 TB/s at 512 keys, 6.35 TB/s at 2048) but give fewer CTAs; without a request
-// from the caller take the longest chunk that still yields about four CTAs per
-// resident slot (2 per SM) when every sequence has max_seqlen keys.
+// Split size.  A CTA has a fixed cost (length lookup, Q load, pipeline fill, cross-warp
+// combine: ~2.8 us), so longer chunks move more bytes per CTA, but the launch still has
+// to fill the machine and ragged batches need several CTAs per slot to balance.  Measured
+// on B200 (bf16, D = 128, GB/s of KV):
+//   many units (batch x KV heads x 16-query-head groups >= 256): 2048 keys is best or within
+//     1 % of best (config 3, ragged: 6290 at 2048, 6120 at 4096, 5560 at 8192; config 5: 6110
+//     at 2048, 5600 at 4096);
+//   few units: the longest chunk that still gives ~256 CTAs (batch 8 x 32768 keys: 6630 at
+//     8192, 5870 at 1024; batch 1 x 131072: 5900 at 4096, 3270 at 512; batch 4, 128 query
+//     heads: 4650 at 2048, 2140 at 256).
 static int decode_chunk(const b200attn_decode_args* a) {
   if (a->chunk_tokens > 0) return a->chunk_tokens;
   const long long group = a->heads_kv > 0 ? a->heads_q / a->heads_kv : 1;
   const long long units = (long long)a->batch * a->heads_kv * ((group + 15) / 16);
   const long long visible = decode_max_visible(a);
-  const int sizes[5] = {2048, 1024, 512, 256, 128};
+  if (units >= 256) return 2048;
+  const int sizes[7] = {8192, 4096, 2048, 1024, 512, 256, 128};
   for (int c : sizes)
-    if (units * ((visible + c - 1) / c) >= 4 * 2 * 148) return c;
+    if (units * ((visible + c - 1) / c) >= 256) return c;
   return 128;
 }
 
