@@ -307,6 +307,52 @@ def run_ours(args, rank, world, local_rank):
         del w5
     except Exception as e:
         other["cfg5_block_sparse_decode"] = {"error": repr(e)}
+    # ---------------- rows either side of the hot path: paged decoding and RMSNorm (HBM bound)
+    try:
+        w3 = workloads.cfg3(dev)
+        page, B3, cap = 64, w3.k_cache.shape[0], w3.k_cache.shape[1]
+        n_pages = B3 * cap // page
+        gperm = torch.Generator(device="cpu").manual_seed(7)
+        table = torch.randperm(n_pages, generator=gperm).to(torch.int32).view(B3, cap // page).to(dev)
+        # scatter the padded caches into pools so that page table[b][i] holds keys i*page.. of sequence b
+        kp = torch.empty(n_pages, page, *w3.k_cache.shape[2:], device=dev, dtype=w3.k_cache.dtype)
+        vp = torch.empty_like(kp)
+        kp[table.view(-1).long()] = w3.k_cache.view(n_pages, page, *w3.k_cache.shape[2:])
+        vp[table.view(-1).long()] = w3.v_cache.view(n_pages, page, *w3.v_cache.shape[2:])
+        fpg = lambda: ops.paged_decode(w3.q, kp, vp, table, w3.seqlens, max_seqlen=w3.max_seqlen)
+        same = bool(torch.equal(fpg(), ops.decode(w3.q, w3.k_cache, w3.v_cache, seqlens=w3.seqlens,
+                                                  max_seqlen=w3.max_seqlen)))
+        msp = reduce_max(time_steps(fpg, max(args.steps, 10), 3, sync, barrier))
+        gbp = w3.kv_bytes / msp / 1e6
+        other["cfg3_paged_decode"] = {
+            "value": gbp * world, "unit": "GB/s", "ms_per_step": msp,
+            "roofline": {"bound": "hbm", "achieved": gbp, "peak": pk["gbs"], "unit": "GB/s", "frac": gbp / pk["gbs"],
+                         "traffic": None, "algorithmic_bytes": w3.kv_bytes},
+            "config": {"workload": "config 3's sequences in 64-key pages scattered at random over a pool, found "
+                                   "through a page table", "bit_identical_to_padded_decode": same}}
+        del w3, kp, vp, table
+    except Exception as e:
+        other["cfg3_paged_decode"] = {"error": repr(e)}
+    try:
+        rows_n, dim_n = 65536, 4096
+        xn = torch.randn(rows_n, dim_n, device=dev, dtype=torch.bfloat16)
+        wn = torch.ones(dim_n, device=dev, dtype=torch.bfloat16)
+        dyn = torch.randn_like(xn)
+        _, rstd_n = ops.rmsnorm_fwd(xn, wn, 1e-6)
+        nbytes = xn.numel() * 2
+        msf = reduce_max(time_steps(lambda: ops.rmsnorm_fwd(xn, wn, 1e-6), max(args.steps, 10), 3, sync, barrier))
+        msb = reduce_max(time_steps(lambda: ops.rmsnorm_bwd(dyn, xn, wn, rstd_n), max(args.steps, 10), 3, sync, barrier))
+        other["rmsnorm_bf16_65536x4096"] = {
+            "value": 2 * nbytes / msf / 1e6 * world, "unit": "GB/s", "ms_per_step": msf,
+            "roofline": {"bound": "hbm", "achieved": 2 * nbytes / msf / 1e6, "peak": pk["gbs"], "unit": "GB/s",
+                         "frac": 2 * nbytes / msf / 1e6 / pk["gbs"], "traffic": None, "algorithmic_bytes": 2 * nbytes},
+            "backward": {"value": 3 * nbytes / msb / 1e6 * world, "unit": "GB/s", "ms_per_step": msb,
+                         "frac": 3 * nbytes / msb / 1e6 / pk["gbs"], "algorithmic_bytes": 3 * nbytes},
+            "config": {"workload": "RMSNorm forward (x in, y out) and backward (dy, x in, dx out) over 65536 rows "
+                                   "of 4096 bf16"}}
+        del xn, wn, dyn, rstd_n
+    except Exception as e:
+        other["rmsnorm_bf16_65536x4096"] = {"error": repr(e)}
     # ---------------- config 1: the reference's own small case (latency bound), in microseconds
     try:
         w1 = workloads.cfg1(dev)
