@@ -451,8 +451,12 @@ decode_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
       if (lane < 16) {
         const int vp = v0 + lane;
         if (vp < c_end) {
-          const int tok = km.to_token(v0 & ~(kBoxTok - 1)) + (lane & (kBoxTok - 1));
-          ok = tok >= 0 && (km.mode == kPaged || tok < km.len);
+          if (km.mode == kPaged) {
+            ok = true;                       // every key below the length is real, wherever its page lies
+          } else {
+            const int tok = km.to_token(v0 & ~(kBoxTok - 1)) + (lane & (kBoxTok - 1));
+            ok = tok >= 0 && tok < km.len;
+          }
         }
       }
       const unsigned vmask = __ballot_sync(0xffffffffu, ok) & 0xffffu;
