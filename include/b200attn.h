@@ -167,7 +167,7 @@ int b200attn_sparse_decode_fwd(const b200attn_decode_args* args, b200attn_stream
  * GPU that loads the library carries those bytes until the process exits.
  *   - A problem whose b200attn_decode_workspace_bytes() exceeds that size is
  *     rejected with B200ATTN_ERR_TOO_LARGE (config 3, B=64 Hq=32 D=128 with
- *     8192-token caches, needs 16.1 MiB and fits).
+ *     8192-token caches, needs 4.0 MiB with the default split and fits).
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current) and keeps it; make
  *     that first call before starting any stream capture.  No call allocates:
