@@ -32,7 +32,7 @@ METRIC = "prefill attn TFLOP/s & decode KV HBM GB/s per B200, at 1/2/4/8 GPUs"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # ncu captures summarised under profiles/ (same workloads as below)
 TRAFFIC = {"cfg2": 409.803520e6 + 120.196096e6, "cfg3": 1.301270e9 + 6.896384e6, "cfg2_backward": 809.810176e6 + 491.803392e6,
-           "cfg4": 554.967296e6 + 121.874176e6, "cfg5": 2.148035e9 + 14.810368e6}
+           "cfg4": 619.421184e6 + 128.075264e6, "cfg5": 2.148035e9 + 14.810368e6}
 WORKLOAD = "cfg2: dense causal prefill bf16 B=4 H=32 S=4096 D=128 per GPU"
 
 
@@ -442,7 +442,8 @@ def run_single(args, dev, sync, barrier, pk):
                                  sparsity=ops.BLOCK_LIST, block_idx=w.block_idx, block_cnt=w.block_cnt)
         work, unit, peak = w.flops / 1e9, "TFLOP/s", pk["tflops"]
     else:
-        w = workloads.cfg5(dev)
+        # (sparse_decode_small: a quarter of config 5's batch, 4.3 GB of cache, for ncu captures)
+        w = workloads.cfg5(dev, B=8) if args.only == "sparse_decode_small" else workloads.cfg5(dev)
         fn = lambda: ops.decode(w.q, w.k_cache, w.v_cache, seqlens=w.seqlens, sparsity=ops.BLOCK_LIST,
                                 block_idx=w.block_idx, block_size=64)
         work, unit, peak = w.kv_bytes / 1e6, "GB/s", pk["gbs"]
@@ -458,7 +459,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="all",
-                    choices=["all", "prefill", "decode", "backward", "sparse_prefill", "sparse_decode"],
+                    choices=["all", "prefill", "decode", "backward", "sparse_prefill", "sparse_decode", "sparse_decode_small"],
                     help="profiling aid: run one kernel's timed loop and print a short line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
