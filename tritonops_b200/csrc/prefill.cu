@@ -651,7 +651,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
               float e0, e1, e2, e3;
               ffma2(e0, e1, __uint_as_float(sr[2 * x]), __uint_as_float(sr[2 * x + 1]), c, neg_mc);
               ffma2(e2, e3, __uint_as_float(sr[2 * x + 2]), __uint_as_float(sr[2 * x + 3]), c, neg_mc);
-              if ((x & 2) == 0) {          // one value in four on the FMA pipe (more measured slower)
+#ifndef B200ATTN_POLY_MASK
+#define B200ATTN_POLY_MASK 2
+#endif
+              if ((x & B200ATTN_POLY_MASK) == 0) {   // one value in four on the FMA pipe (more measured slower)
                 exp2_fma_pair(e0, e1, e0, e1);
               } else {
                 e0 = ex2(e0); e1 = ex2(e1);
@@ -850,7 +853,10 @@ int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       return B200ATTN_ERR_CUDA;
-    p.prefetch_ahead = sms;   // one CTA per SM
+#ifndef B200ATTN_PREFETCH_WAVES
+#define B200ATTN_PREFETCH_WAVES 1
+#endif
+    p.prefetch_ahead = sms * B200ATTN_PREFETCH_WAVES;   // one CTA per SM
   }
   const bool window = sparse && a->sparsity == B200ATTN_WINDOW;
   p.causal = window ? 1 : (a->causal ? 1 : 0);
