@@ -96,9 +96,10 @@ def _i32(t: Optional[Tensor], dev) -> Optional[Tensor]:
 # --------------------------------------------------------------------------
 # decoding
 # --------------------------------------------------------------------------
-def decode_workspace_bytes(batch, heads_q, head_dim, max_visible, chunk=0) -> int:
-    a = DecodeArgs(batch=batch, heads_q=heads_q, heads_kv=1, head_dim=head_dim,
-                   max_seqlen=max_visible, chunk_tokens=chunk, sparsity=DENSE)
+def decode_workspace_bytes(batch, heads_q, heads_kv, head_dim, max_seqlen, chunk=0) -> int:
+    """Scratch bytes dense decoding needs for this shape (the split size, when 0, depends on all of them)."""
+    a = DecodeArgs(batch=batch, heads_q=heads_q, heads_kv=heads_kv, head_dim=head_dim,
+                   max_seqlen=max_seqlen, chunk_tokens=chunk, sparsity=DENSE)
     return _lib.lib().b200attn_decode_workspace_bytes(C.byref(a))
 
 
