@@ -97,7 +97,7 @@ def test_decode_workspace_formula(lib):
     assert lib.b200attn_decode_workspace_bytes(C.byref(a)) == rows * 128 * 4 + rows * 4
     a.chunk_tokens = 0                        # automatic: 2048-key chunks for this size
     assert lib.b200attn_decode_workspace_bytes(C.byref(a)) == 64 * 32 * 4 * (128 * 4 + 4)
-    a.batch = 1                               # few units: the longest chunk that still gives ~256 CTAs (256 keys)
+    a.batch = 1                               # few units (8): the longest chunk that still gives 148 CTAs (256 keys)
     assert lib.b200attn_decode_workspace_bytes(C.byref(a)) == 1 * 32 * 32 * (128 * 4 + 4)
     a.max_seqlen = 131072                     # ... which is 4096 keys for one long sequence
     assert lib.b200attn_decode_workspace_bytes(C.byref(a)) == 1 * 32 * 32 * (128 * 4 + 4)

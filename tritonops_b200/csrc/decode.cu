@@ -630,9 +630,11 @@ static int decode_max_visible(const b200attn_decode_args* a) {
 //   many units (batch x KV heads x 16-query-head groups >= 256): 2048 keys is best or within
 //     1 % of best (config 3, ragged: 6290 at 2048, 6120 at 4096, 5560 at 8192; config 5: 6110
 //     at 2048, 5600 at 4096);
-//   few units: the longest chunk that still gives ~256 CTAs (batch 8 x 32768 keys: 6630 at
-//     8192, 5870 at 1024; batch 1 x 131072: 5900 at 4096, 3270 at 512; batch 4, 128 query
-//     heads: 4650 at 2048, 2140 at 256).
+//   few units: the longest power-of-two chunk that still gives one CTA per SM (batch 8 x 32768
+//     keys: 6630 at 8192, 5870 at 1024; batch 1 x 131072: 5900 at 4096, 3270 at 512; batch 4, 128
+//     query heads: 4650 at 2048, 2140 at 256; batch 3 x 20000: 4980 at 2048, 4310 at 1024).
+//     Chunks cut to fill exactly one wave of 296 CTAs (e.g. 3584 keys) measured 4-7 % slower
+//     than the neighbouring power of two.
 static int decode_chunk(const b200attn_decode_args* a) {
   if (a->chunk_tokens > 0) return a->chunk_tokens;
   const long long group = a->heads_kv > 0 ? a->heads_q / a->heads_kv : 1;
@@ -641,7 +643,7 @@ static int decode_chunk(const b200attn_decode_args* a) {
   if (units >= 256) return 2048;
   const int sizes[7] = {8192, 4096, 2048, 1024, 512, 256, 128};
   for (int c : sizes)
-    if (units * ((visible + c - 1) / c) >= 256) return c;
+    if (units * ((visible + c - 1) / c) >= 148) return c;   // at least one CTA per SM
   return 128;
 }
 
