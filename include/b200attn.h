@@ -5,7 +5,22 @@
  * never throws: it returns 0 or a negative b200attn_status.  All pointers are
  * device pointers that stay owned by the caller and must stay valid until the
  * stream has run the launch.  Strides are in ELEMENTS of the tensor's dtype;
- * the innermost (head_dim) stride is always 1.
+ * the innermost (head_dim) stride is always 1.  Q, K, V and O share one
+ * head_dim (the reference wrappers take a separate width for V,
+ * flash_attn_decoding.py:233-236, but allocate O with Q's, flash_attn_triton.py:608).
+ *
+ * Threads and devices: calls are re-entrant and may come from any host
+ * thread; the library keeps no state beyond read-only per-device facts looked
+ * up once under std::call_once.  Every launcher checks, after its arguments,
+ * that the current device is compute capability 10.x and answers
+ * B200ATTN_ERR_DEVICE otherwise (the reference only probes for Hopper,
+ * utils/utils.py:19-24).  B200ATTN_ASSUME_CC_MAJOR=<n> in the environment
+ * replaces the probed major version, so that refusal can be exercised on a
+ * machine whose GPUs are all sm_100.
+ *
+ * Device-side waits are bounded: a kernel whose wait on a copy or a product
+ * gives up drains, returns normally and sets *status_word (where the argument
+ * struct has one and it is not NULL); its outputs are then invalid.
  *
  * Each function names the reference interface (rookie-joe/TritonOps,
  * path:line inside that project) it stands in for.
@@ -70,7 +85,8 @@ typedef struct {
   int32_t dtype;              /* b200attn_dtype */
   int32_t batch, heads_q, heads_kv, head_dim;
   int32_t seqlen;             /* fixed-length form: tokens per sequence */
-  int32_t max_seqlen;         /* varlen form: upper bound on cu[b+1]-cu[b] (sizes the grid) */
+  int32_t max_seqlen;         /* varlen form: upper bound on cu[b+1]-cu[b]; it sizes the grid, and a longer
+                                 sequence is cut at ceil(max_seqlen / 256) * 256 tokens */
   int64_t total_tokens;       /* varlen form: rows in the packed arrays */
   const int32_t* cu_seqlens;  /* nullable, see above */
   int64_t q_stride_b, q_stride_t, q_stride_h;
@@ -119,7 +135,7 @@ typedef struct {
   void* o;
   int32_t dtype;
   int32_t batch, heads_q, heads_kv, head_dim;
-  int32_t max_seqlen;         /* upper bound on the lengths (<= cache capacity) */
+  int32_t max_seqlen;         /* upper bound on the lengths (<= cache capacity); a longer length is cut there */
   const int32_t* cu_seqlens;  /* nullable */
   const int32_t* seqlens;     /* nullable */
   int64_t q_stride_b, q_stride_h;
@@ -138,7 +154,8 @@ typedef struct {
   int32_t max_sel;
   void* workspace;
   size_t workspace_bytes;
-  int32_t* status_word;       /* nullable, reserved */
+  int32_t* status_word;       /* nullable; device int set to 1 if a bounded wait of the split kernel gave up
+                                 (the chunks it could not finish count as empty) */
 } b200attn_decode_args;
 
 /* Bytes of scratch b200attn_decode_fwd / b200attn_sparse_decode_fwd need. */
@@ -209,7 +226,7 @@ typedef struct {
   int32_t chunk_tokens;        /* as in b200attn_decode_args */
   void* workspace;
   size_t workspace_bytes;
-  int32_t* status_word;        /* nullable, reserved */
+  int32_t* status_word;        /* nullable; as in b200attn_decode_args */
 } b200attn_paged_decode_args;
 
 size_t b200attn_paged_decode_workspace_bytes(const b200attn_paged_decode_args* args);
@@ -327,7 +344,10 @@ size_t b200attn_prefill_bwd_workspace_bytes(const b200attn_prefill_bwd_args* arg
 
 /* dQ, dK, dV of the dense causal / non-causal forward.  Replaces
  * flash_attn_triton_bwd (flash_attn_triton/flash_attn_triton.py:661-813) and
- * its kernels (:184-592). */
+ * its kernels (:184-592).  dK and dV are summed in a fixed order and repeat
+ * bit for bit; dQ is summed in fp32 by reduce-adds whose order is not fixed
+ * (the reference's separate dQ kernel, :255-410, is deterministic), so two
+ * runs may differ in the last bit of the 16-bit result. */
 int b200attn_prefill_bwd(const b200attn_prefill_bwd_args* args, b200attn_stream_t stream);
 
 /* ------------------------------------------------------------------------

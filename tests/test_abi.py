@@ -218,3 +218,65 @@ def test_new_entry_points_validate_before_touching_the_device(lib):
     assert L.b200attn_rmsnorm_bwd(C.byref(_lib.RmsNormBwdArgs()), None) == -1
     assert L.b200attn_rmsnorm_bwd_workspace_bytes(C.byref(_lib.RmsNormBwdArgs(rows=1000, dim=4096))) == 592 * 4096 * 4
     assert L.b200attn_paged_decode_workspace_bytes(C.byref(d)) == 0
+
+
+def test_head_dim_mismatch_is_rejected_before_any_launch(lib):
+    """One head_dim for Q, K, V: a narrower V (which the reference wrapper lets through,
+    flash_attn_decoding.py:233-236) must raise in Python, before any pointer reaches a kernel."""
+    import torch
+    from tritonops_b200 import ops
+    q = torch.zeros(2, 4, 64, dtype=torch.float16)
+    kc = torch.zeros(2, 16, 2, 64, dtype=torch.float16)
+    vc = torch.zeros(2, 16, 2, 32, dtype=torch.float16)
+    sl = torch.tensor([16, 16], dtype=torch.int32)
+    with pytest.raises(ValueError, match="share head_dim"):
+        ops.decode(q, kc, vc, seqlens=sl)
+    with pytest.raises(ValueError, match="share head_dim"):
+        ops.paged_decode(q, kc, vc, torch.zeros(2, 1, dtype=torch.int32), sl)
+    qp, kp, vp = torch.zeros(1, 16, 4, 64, dtype=torch.float16), torch.zeros(1, 16, 2, 64, dtype=torch.float16), \
+        torch.zeros(1, 16, 2, 32, dtype=torch.float16)
+    with pytest.raises(ValueError, match="share head_dim"):
+        ops.prefill(qp, kp, vp)
+    with pytest.raises(ValueError, match="share head_dim"):
+        ops.prefill_bwd(qp, kp, kp, qp, torch.zeros(1, 16, 4, 32, dtype=torch.float16), torch.zeros(1, 16, 4))
+
+
+def test_valid_call_without_a_device_reports_cuda_error(lib):
+    """Arguments that pass validation reach the device probe; with no CUDA device it answers
+    B200ATTN_ERR_CUDA (never run where a device exists: the pointers are made up)."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    from tritonops_b200 import _lib
+    a = _lib.RmsNormFwdArgs(0x1000, 0x1000, 0x2000, None, _lib.BF16, _lib.BF16, 4, 64, 64, 64, 1e-6)
+    assert lib.b200attn_rmsnorm_fwd(C.byref(a), None) == -10
+
+
+@pytest.mark.gpu
+def test_wrong_architecture_is_refused():
+    """B200ATTN_ERR_DEVICE: every launcher probes the current device once (the counterpart of the
+    reference's arch probe, utils/utils.py:19-24) and refuses anything but compute capability
+    10.x.  All GPUs here are sm_100, so a child process is told to assume another architecture."""
+    import subprocess
+    import sys
+    code = (
+        "import torch\n"
+        "from tritonops_b200 import ops\n"
+        "x = torch.randn(4, 64, device='cuda', dtype=torch.bfloat16)\n"
+        "w = torch.ones(64, device='cuda', dtype=torch.bfloat16)\n"
+        "q = torch.randn(2, 4, 64, device='cuda', dtype=torch.float16)\n"
+        "kc = torch.randn(2, 64, 2, 64, device='cuda', dtype=torch.float16)\n"
+        "sl = torch.tensor([64, 10], dtype=torch.int32, device='cuda')\n"
+        "n = 0\n"
+        "for f in (lambda: ops.rmsnorm_fwd(x, w, 1e-6), lambda: ops.decode(q, kc, kc, seqlens=sl),\n"
+        "          lambda: ops.prefill(kc[:1], kc[:1], kc[:1])):\n"
+        "    try:\n"
+        "        f()\n"
+        "    except RuntimeError as e:\n"
+        "        assert 'status -12' in str(e) and 'compute capability' in str(e), str(e)\n"
+        "        n += 1\n"
+        "print('refused', n)\n")
+    env = dict(os.environ, B200ATTN_ASSUME_CC_MAJOR="9", PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert "refused 3" in out.stdout

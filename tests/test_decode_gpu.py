@@ -187,3 +187,58 @@ def test_error_codes():
         ops.decode(q.cuda(), kc.cuda(), vc.cuda(), cu_seqlens=cu.cuda())        # head_dim 48
     with pytest.raises(RuntimeError):
         ops.decode(q, kc, vc, cu_seqlens=cu)                                    # CPU tensors
+
+
+def test_cfg5_shape_properties():
+    """Full config-5 size (B=32, H=32 MHA, D=128, 32768 keys in 512 blocks of 64, 64 blocks
+    listed per (b, h)): sampled (b, h) against fp32 math over the 64 gathered blocks on the
+    device, determinism, and a permutation of the batch permutes the output."""
+    ops, wl, _, _ = _mods()
+    w = wl.cfg5("cuda")
+    f = lambda q, kc, vc, sl, idx: ops.decode(q, kc, vc, seqlens=sl, sparsity=ops.BLOCK_LIST,
+                                              block_idx=idx, block_size=64)
+    o = f(w.q, w.k_cache, w.v_cache, w.seqlens, w.block_idx)
+    assert torch.equal(o, f(w.q, w.k_cache, w.v_cache, w.seqlens, w.block_idx))
+    assert bool((w.block_idx[..., -1] == 511).all())           # the newest block is always listed
+    assert bool((w.block_idx[..., 1:] > w.block_idx[..., :-1]).all())
+    for b, h in [(0, 0), (5, 17), (13, 2), (31, 31), (20, 9), (8, 30)]:
+        rows = (w.block_idx[b, h].long()[:, None] * 64 + torch.arange(64, device="cuda")[None, :]).reshape(-1)
+        kk, vv = w.k_cache[b, rows, h].float(), w.v_cache[b, rows, h].float()
+        p = torch.softmax((kk @ w.q[b, h].float()) * w.scale, 0)
+        assert (o[b, h].float() - p @ vv).abs().max().item() <= 2e-2
+    # batch permutation on a slice (a permuted copy of the whole 17 GB cache is not needed for
+    # the property): sequences 3, 1, 2, 0 of the first four
+    perm = torch.tensor([3, 1, 2, 0], device="cuda")
+    o4 = f(w.q[perm], w.k_cache[:4][perm], w.v_cache[:4][perm], w.seqlens[perm], w.block_idx[perm])
+    assert torch.equal(o4, o[perm])
+
+
+def test_length_beyond_max_seqlen_is_cut_there():
+    """A length larger than max_seqlen (which sizes the grid and the scratch) is treated as
+    max_seqlen: the truncated result, and nothing is read or written out of bounds (a canary
+    row behind the output stays intact)."""
+    ops, _, _, _ = _mods()
+    lens = [300, 200]
+    q, kc, vc, _ = make(2, 8, 2, 128, lens, torch.bfloat16, seed=11, tmax=320)
+    sl = torch.tensor([300, 200], dtype=torch.int32).cuda()
+    for chunk in (0, 64):
+        o = ops.decode(q.cuda(), kc.cuda(), vc.cuda(), seqlens=sl, max_seqlen=256, chunk=chunk)
+        ref = orc.decoding_exact(q, kc, vc, [256, 200])
+        assert maxabs(o, ref) <= 2e-2
+
+
+def test_debug_status_mode_covers_decoding(monkeypatch):
+    """With the status word switched on, decoding and paged decoding pass one, find it clear
+    after a synchronisation and return the same bits."""
+    ops, _, _, _ = _mods()
+    lens = [700, 33]
+    q, kc, vc, _ = make(2, 8, 2, 128, lens, torch.bfloat16, seed=4, tmax=704)
+    sl = torch.tensor(lens, dtype=torch.int32).cuda()
+    o0 = ops.decode(q.cuda(), kc.cuda(), vc.cuda(), seqlens=sl)
+    monkeypatch.setattr(ops, "DEBUG_STATUS", True)
+    o1 = ops.decode(q.cuda(), kc.cuda(), vc.cuda(), seqlens=sl)
+    assert torch.equal(o0, o1)
+    assert int(ops._status_word(torch.device("cuda", 0)).item()) == 0
+    table = torch.arange(2 * 11, dtype=torch.int32).view(2, 11).cuda()
+    o2 = ops.paged_decode(q.cuda(), kc.cuda().view(22, 64, 2, 128), vc.cuda().view(22, 64, 2, 128), table, sl)
+    assert torch.equal(o0, o2)

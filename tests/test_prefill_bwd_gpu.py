@@ -131,3 +131,59 @@ def test_bwd_linearity_at_full_head_size():
     close(ga[0][0, sl, h], qq.grad, 2e-2)
     close(ga[1][0, sl, h], kk.grad, 2e-2)
     close(ga[2][0, sl, h], vv.grad, 3e-2)
+
+
+def test_bwd_rows_after_a_sequence_never_reach_its_gradients():
+    """Forward outputs aside, the backward contracts over query rows (dK, dV) and key rows (dQ)
+    of tiles that reach past the sequence end; NaN / Inf in the rows that follow a sequence must
+    not reach its gradients (the reference zero-pads those loads, flash_attn_triton.py:304-330)."""
+    ops, _ = _mods()
+    lens = [300, 200]
+    q, k, v, do, cu = make(lens, 4, 2, 128, torch.bfloat16, seed=31)
+    cud = cu.cuda()
+
+    def run(q, k, v, do):
+        q, k, v, do = (t.cuda() for t in (q, k, v, do))
+        o, lse = ops.prefill(q, k, v, cu_seqlens=cud, max_seqlen=300)
+        return ops.prefill_bwd(q, k, v, o, do, lse, cu_seqlens=cud, max_seqlen=300)
+
+    ga = run(q, k, v, do)
+    q2, k2, v2, do2 = (t.clone() for t in (q, k, v, do))
+    for t in (q2, k2, v2, do2):
+        t[0, 300:] = float("nan")
+    gb = run(q2, k2, v2, do2)
+    for a, b_ in zip(ga, gb):
+        assert torch.isfinite(b_[0, :300].float()).all()
+    # dK and dV of a key tile are sums in a fixed order: bit-equal.  dQ rows are sums of
+    # reduce-adds whose order varies: compared within the run-to-run tolerance.
+    assert torch.equal(ga[1][0, :300], gb[1][0, :300]) and torch.equal(ga[2][0, :300], gb[2][0, :300])
+    close(gb[0][0, :300], ga[0][0, :300], 2e-2)
+
+
+def test_bwd_at_config2_size_and_run_to_run_behaviour():
+    """Config 2 (B=4, H=32, S=4096, D=128 causal bf16) through the backward: sampled heads of dQ,
+    dK, dV against fp32 autograd on the device.  Run twice: dK and dV are accumulated in tensor
+    memory in a fixed order and must be bit-equal; dQ is summed by reduce-adds whose arrival
+    order is not fixed (the reference's separate dQ kernel, flash_attn_triton.py:255-410, is
+    deterministic), so its two runs may differ in the last bits: bounded here by 2^-7 relative
+    to the tensor's largest magnitude (one bf16 ulp) on every element."""
+    ops, _ = _mods()
+    from tritonops_b200 import workloads
+    w = workloads.cfg2("cuda")
+    S, D = 4096, 128
+    do = torch.randn(w.q.shape, device="cuda", dtype=torch.float32, generator=torch.Generator("cuda").manual_seed(7)).to(w.q.dtype)
+    o, lse = ops.prefill(w.q, w.k, w.v, cu_seqlens=w.cu_seqlens, max_seqlen=S)
+    g1 = ops.prefill_bwd(w.q, w.k, w.v, o, do, lse, cu_seqlens=w.cu_seqlens, max_seqlen=S)
+    g2 = ops.prefill_bwd(w.q, w.k, w.v, o, do, lse, cu_seqlens=w.cu_seqlens, max_seqlen=S)
+    assert torch.equal(g1[1], g2[1]) and torch.equal(g1[2], g2[2])
+    dq_gap = (g1[0].float() - g2[0].float()).abs().max().item()
+    assert dq_gap <= g1[0].float().abs().max().item() * 2 ** -7
+    tril = torch.ones(S, S, dtype=torch.bool, device="cuda").tril()
+    for b, h in [(0, 0), (2, 19), (3, 31)]:
+        sl = slice(b * S, (b + 1) * S)
+        qq, kk, vv = (t[0, sl, h].float().requires_grad_(True) for t in (w.q, w.k, w.v))
+        s_ = ((qq @ kk.T) * D ** -0.5).masked_fill(~tril, float("-inf"))
+        (torch.softmax(s_, -1) @ vv * do[0, sl, h].float()).sum().backward()
+        close(g1[0][0, sl, h], qq.grad, 2e-2)
+        close(g1[1][0, sl, h], kk.grad, 2e-2)
+        close(g1[2][0, sl, h], vv.grad, 3e-2)

@@ -303,3 +303,47 @@ def test_cfg4_shape_properties():
             ref = torch.softmax(s, -1) @ w.v[0, sl, h].float()
             assert (o[0, sl, h][rs].float() - ref).abs().max().item() <= 2e-2
             assert (lse[0, sl, h][rs] - torch.logsumexp(s, -1)).abs().max().item() <= 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("mode", ["dense", "noncausal", "window", "blocks"])
+def test_rows_after_a_sequence_never_reach_its_output(dtype, mode):
+    """The reference loads every tile with zero padding past the sequence end
+    (flash_attn_triton.py:155-165), so whatever follows a sequence in the packed arrays cannot
+    reach its output.  Here the second sequence is first real data, then NaN / Inf: the first
+    sequence's O and LSE must not change by a bit and must stay finite."""
+    ops, _, _, sp = _mods()
+    lens = [300, 200]                      # 300 = 2 * 128 + 44: the last KV tile holds 84 foreign rows
+    q, k, v, cu = make(lens, 4, 2, 128, dtype, seed=21)
+
+    def run(q, k, v):
+        kw = dict(cu_seqlens=cu.cuda(), max_seqlen=300)
+        if mode == "window":
+            kw.update(sparsity=ops.WINDOW, window_local=100, window_global=64)
+        elif mode == "blocks":
+            idx, cnt = _random_lists(lens, 4, 0.5, seed=2)
+            kw.update(sparsity=ops.BLOCK_LIST, block_idx=idx.cuda(), block_cnt=cnt.cuda())
+        elif mode == "noncausal":
+            kw.update(causal=False)
+        return ops.prefill(q.cuda(), k.cuda(), v.cuda(), **kw)
+
+    o_a, lse_a = run(q, k, v)
+    q2, k2, v2 = q.clone(), k.clone(), v.clone()
+    q2[0, 300:] = float("nan")
+    k2[0, 300:] = float("inf")
+    v2[0, 300:] = float("nan")
+    o_b, lse_b = run(q2, k2, v2)
+    assert torch.isfinite(o_b[0, :300].float()).all() and torch.isfinite(lse_b[0, :300]).all()
+    assert torch.equal(o_a[0, :300], o_b[0, :300]) and torch.equal(lse_a[0, :300], lse_b[0, :300])
+
+
+def test_sequence_longer_than_max_seqlen_is_cut_there():
+    """max_seqlen sizes the grid; a longer sequence is attended over its first
+    ceil(max_seqlen / 256) * 256 tokens only, and nothing outside is read as a key."""
+    ops, _, _, _ = _mods()
+    q, k, v, cu = make([700], 2, 2, 64, torch.float16, seed=6)
+    o, lse = ops.prefill(q.cuda(), k.cuda(), v.cuda(), cu_seqlens=cu.cuda(), max_seqlen=500, causal=False)
+    cu_cut = torch.tensor([0, 512], dtype=torch.int32)
+    ref, rl = orc.dense_prefill_exact(q[:, :512], k[:, :512], v[:, :512], cu_cut, causal=False)
+    assert maxabs(o[:, :512], ref) <= 5e-3
+    assert maxabs(lse[:, :512], rl) <= 2e-3

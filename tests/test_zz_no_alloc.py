@@ -59,6 +59,10 @@ def test_noalloc_matches_workspace_entry_point_twice():
         assert torch.cuda.memory_allocated() == before
         # same kernels on the same inputs: identical bits, well inside the bf16 tolerance of 2e-2
         assert torch.equal(o_na, o_ws)
+        # ... and both are the right answer: fp32 softmax(q K^T scale) V on the same rounded inputs
+        from oracle import attention_oracle as orc
+        ref = orc.decoding_exact(q.cpu(), kc.cpu(), vc.cpu(), lens.cpu().tolist())
+        assert (o_na.float().cpu() - ref).abs().max().item() <= 2e-2
 
 
 def test_noalloc_rejects_oversized_problem():

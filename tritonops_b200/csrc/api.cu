@@ -1,10 +1,39 @@
 // extern "C" surface of libb200attn.so; declarations and the reference
 // interfaces they replace are in include/b200attn.h.
+#include <stdlib.h>
+
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200attn {
 static thread_local int g_launch_count = 0;
 void set_launch_count(int n) { g_launch_count = n; }
+
+int device_info(const DeviceInfo** info) {
+  constexpr int kMaxDevices = 64;
+  static std::once_flag once[kMaxDevices];
+  static DeviceInfo infos[kMaxDevices];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200ATTN_ERR_CUDA;
+  std::call_once(once[dev], [dev] {
+    int major = 0, sms = 0;
+    DeviceInfo& d = infos[dev];
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+      d.status = B200ATTN_ERR_CUDA;
+      return;
+    }
+    // B200ATTN_ASSUME_CC_MAJOR=<n> stands in for the probed value: the only way to see the
+    // refusal path on a machine whose GPUs are all sm_100
+    if (const char* e = getenv("B200ATTN_ASSUME_CC_MAJOR")) major = atoi(e);
+    d.sm_count = sms;
+    d.status = major == 10 ? B200ATTN_OK : B200ATTN_ERR_DEVICE;
+  });
+  if (infos[dev].status != B200ATTN_OK) return infos[dev].status;
+  if (info) *info = &infos[dev];
+  return B200ATTN_OK;
+}
 }  // namespace b200attn
 
 using namespace b200attn;

@@ -80,6 +80,7 @@ int window_blocks_prefill(const b200attn_window_blocks_prefill_args* a, cudaStre
   const long long rows = (long long)a->batch * a->heads * a->n_qblocks;
   const long long ctas = (rows + 3) / 4;
   if (ctas > 0x7fffffffLL) return B200ATTN_ERR_TOO_LARGE;
+  if (int dst = device_info(nullptr)) return dst;
   set_launch_count(1);
   window_blocks_prefill_kernel<<<(unsigned)ctas, 128, 0, stream>>>(*a);
   return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
@@ -113,6 +114,7 @@ int window_blocks_decode(const b200attn_window_blocks_decode_args* a, cudaStream
   if (a->batch <= 0 || a->heads_kv <= 0 || a->max_sel <= 0 || a->block_size <= 0) return B200ATTN_ERR_SHAPE;
   if (a->window_local < 0 || a->window_global < 0) return B200ATTN_ERR_MODE;
   const long long rows = (long long)a->batch * a->heads_kv;
+  if (int dst = device_info(nullptr)) return dst;
   set_launch_count(1);
   window_blocks_decode_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>(*a);
   return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
@@ -240,6 +242,7 @@ int topk_blocks(const b200attn_topk_blocks_args* a, cudaStream_t stream) {
     return B200ATTN_ERR_SHAPE;
   if (a->force_first < 0 || a->force_last < 0) return B200ATTN_ERR_MODE;
   if (a->n_blocks > kTopkMaxBlocks) return B200ATTN_ERR_TOO_LARGE;
+  if (int dst = device_info(nullptr)) return dst;
   set_launch_count(1);
   topk_blocks_kernel<<<a->rows, kTopkThreads, (size_t)a->n_blocks * 4, stream>>>(*a);
   return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;

@@ -12,6 +12,16 @@ namespace b200attn {
 
 void set_launch_count(int n);
 
+// Facts about the current device, looked up once per device (std::call_once) and read-only
+// afterwards: launchers are re-entrant and keep no other global state.
+struct DeviceInfo {
+  int status;    // B200ATTN_OK, or B200ATTN_ERR_DEVICE when the device is not compute capability 10.x
+  int sm_count;
+};
+// B200ATTN_OK and *info, B200ATTN_ERR_DEVICE (wrong architecture: the kernels are sm_100a only, the
+// counterpart of the reference's arch probe, utils/utils.py:19-24) or B200ATTN_ERR_CUDA (no device).
+int device_info(const DeviceInfo** info);
+
 // implemented in decode.cu / prefill.cu, called by api.cu
 size_t decode_workspace_bytes(const b200attn_decode_args* a);
 int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t scratch_bytes,

@@ -50,6 +50,8 @@ struct DecodeParams {
   int chunk, max_chunks;
   int sparsity, win_global, win_local, block_size, max_sel;
   int head_dim_rt;
+  int max_seqlen;     // lengths beyond it are cut there (the grid and the scratch are sized for it)
+  int* status_word;   // nullable: set to 1 when a bounded wait of the split kernel gave up
   float scale_log2;
   long long map_keys;  // host only: key extent and batch extent of the cache's tensor maps
   int map_batch;
@@ -81,7 +83,7 @@ __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
 
 __device__ __forceinline__ KeyMap make_keymap(const DecodeParams& p, int b, int hk) {
   KeyMap m;
-  m.len = max(seq_len_of(p, b), 0);
+  m.len = min(max(seq_len_of(p, b), 0), p.max_seqlen);
   m.mode = p.sparsity;
   m.split = 0; m.shift = 0; m.bsize = 1; m.bshift = 0; m.blocks = nullptr;
   if (p.sparsity == 0) {
@@ -400,9 +402,10 @@ decode_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     // ================================================================ producer
     if (lane == 0) {
       prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
-      for (int tile = 0; tile < n_tiles; ++tile) {
+      int issued = 0;
+      for (int tile = 0; tile < n_tiles; ++tile, ++issued) {
         const int s = tile % L::kStages;
-        mbar_wait(empty(s), ((tile / L::kStages) & 1) ^ 1, abort_flag);
+        if (!mbar_wait(empty(s), ((tile / L::kStages) & 1) ^ 1, abort_flag)) break;
         const int v0 = c_begin + tile * kStageTok;
         const int nbox = min(kStageTok / kBoxTok, (c_end - v0 + kBoxTok - 1) / kBoxTok);
         mbar_expect_tx(full(s), nbox * 2 * L::kPanels * kBoxTok * 128);
@@ -416,6 +419,11 @@ decode_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
           }
         }
       }
+      // A wait gave up somewhere in the CTA: the consumers no longer wait for the stages, so
+      // the copies still in flight are waited for here before the CTA may exit.
+      if (*abort_flag)
+        for (int tile = max(issued - L::kStages, 0); tile < issued; ++tile)
+          mbar_drain(full(tile % L::kStages), (tile / L::kStages) & 1);
     }
     return;
   }
@@ -442,7 +450,7 @@ decode_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
 
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int s = tile % L::kStages;
-    mbar_wait(full(s), (tile / L::kStages) & 1, abort_flag);
+    if (!mbar_wait(full(s), (tile / L::kStages) & 1, abort_flag)) break;   // reported below
     const int v0 = c_begin + tile * kStageTok + 16 * warp;   // this warp's 16 keys of the stage
     if (v0 < c_end) {
       const uint32_t ktile = sbase + s * L::kStageBytes, vtile = ktile + L::kTileBytes;
@@ -547,6 +555,21 @@ decode_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
   asm volatile("bar.sync 1, 128;" ::: "memory");
+  const int heads_here = min(16, p.group - gg * 16);
+  const int D = p.head_dim_rt;
+  if (*abort_flag) {
+    // A bounded wait gave up (flash_attn_decoding.py has no counterpart: its loads cannot
+    // stall).  The ring may still be receiving copies, so it is not reused as the combine
+    // buffer: the chunk is reported as empty and the caller is told through the status word.
+    for (int idx = threadIdx.x; idx < heads_here * D; idx += 128) {
+      const int g = idx / D, d = idx - g * D;
+      const long long row = ((long long)b * p.heads_q + hk * p.group + gg * 16 + g) * p.max_chunks + chunk_id;
+      p.part_o[row * D + d] = 0.f;
+      if (d == 0) p.part_lse[row] = -INFINITY;
+    }
+    if (threadIdx.x == 0 && p.status_word) atomicExch(p.status_word, 1);
+    return;
+  }
   float* sm_o = reinterpret_cast<float*>(sgen);                       // [4][16][DP + 1]
   float* sm_m = sm_o + 4 * 16 * L::kCombinePitch;                      // [4][16]
   float* sm_l = sm_m + 4 * 16;
@@ -562,8 +585,6 @@ decode_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     r1[0] = acc[i][2]; r1[1] = acc[i][3];
   }
   asm volatile("bar.sync 1, 128;" ::: "memory");
-  const int heads_here = min(16, p.group - gg * 16);
-  const int D = p.head_dim_rt;
   for (int idx = threadIdx.x; idx < heads_here * D; idx += 128) {
     const int g = idx / D, d = idx - g * D;
     float M = -INFINITY;
@@ -781,6 +802,8 @@ static int decode_fwd_impl(const b200attn_decode_args* a, bool sparse, long long
   size_t need = decode_workspace_bytes(&eff);
   if (!ws || ws_bytes < need) return scratch ? B200ATTN_ERR_TOO_LARGE : B200ATTN_ERR_WORKSPACE;
   if ((uintptr_t)ws & 15) return B200ATTN_ERR_ALIGN;
+  st = device_info(nullptr);
+  if (st != B200ATTN_OK) return st;
 
   DecodeParams p;
   p.q = a->q; p.k = a->k_cache; p.v = a->v_cache; p.o = a->o;
@@ -801,6 +824,8 @@ static int decode_fwd_impl(const b200attn_decode_args* a, bool sparse, long long
   p.block_size = a->block_size; p.max_sel = a->max_sel;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.head_dim_rt = a->head_dim;
+  p.max_seqlen = a->max_seqlen;
+  p.status_word = a->status_word;
   // keys beyond max_seqlen are never visible; the copy engine zero-fills past the extent
   p.map_keys = pool_keys > 0 ? pool_keys : a->max_seqlen;
   p.map_batch = pool_keys > 0 ? 1 : a->batch;

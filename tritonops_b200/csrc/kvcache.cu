@@ -66,6 +66,7 @@ int kv_pack_to_cache(const b200attn_kv_pack_args* a, cudaStream_t stream) {
   const int wpb = 8;
   const long long blocks = (rows + wpb - 1) / wpb;
   if (blocks > 0x7fffffffLL) return B200ATTN_ERR_TOO_LARGE;
+  if (int dst = device_info(nullptr)) return dst;
   pack_to_cache_kernel<<<(unsigned)blocks, wpb * 32, 0, stream>>>(
       (const uint4*)a->packed, (uint4*)a->cache, a->cu_seqlens, a->packed_stride_t / 8, a->packed_stride_h / 8,
       a->cache_stride_b / 8, a->cache_stride_t / 8, a->cache_stride_h / 8, a->batch, a->capacity, a->heads,
@@ -86,6 +87,7 @@ int kv_append(const b200attn_kv_append_args* a, cudaStream_t stream) {
     if (s % 8 != 0 || s < 0) return B200ATTN_ERR_STRIDE;
   const long long rows = (long long)a->batch * a->heads;
   const int wpb = 8;
+  if (int dst = device_info(nullptr)) return dst;
   append_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, stream>>>(
       (const uint4*)a->new_k, (const uint4*)a->new_v, (uint4*)a->k_cache, (uint4*)a->v_cache, a->seqlens,
       a->new_stride_b / 8, a->new_stride_h / 8, a->cache_stride_b / 8, a->cache_stride_t / 8,

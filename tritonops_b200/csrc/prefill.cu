@@ -20,6 +20,7 @@
 // the other tile, so MMA and exponentials overlap.  TMEM columns: S0 [0,128),
 // S1 [128,256), O0 [256,256+D), O1 [384,384+D); P_t aliases the first half of S_t.
 // Every mbarrier wait is bounded; a timeout sets *status_word and the CTA drains.
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -112,29 +113,6 @@ __device__ __forceinline__ bool tile_needs_mask(const PrefillParams& p, int q0t,
   return !full;
 }
 
-#ifdef B200ATTN_TRACE
-// Debug builds only: event trace (event id, SM clock) of one heavy CTA.
-__device__ unsigned int g_trace_n;
-__device__ unsigned long long g_trace[1 << 16];
-__device__ __forceinline__ void trace_ev(int id) {
-  if (blockIdx.x != 16 * 40) return;   // one CTA with the longest KV loop
-  long long c;
-  asm volatile("mov.u64 %0, %%clock64;" : "=l"(c)::"memory");
-  unsigned int i = atomicAdd(&g_trace_n, 1u);
-  if (i < (1u << 16)) g_trace[i] = ((unsigned long long)id << 48) | ((unsigned long long)c & 0xffffffffffffULL);
-}
-#define TRACE(id) trace_ev(id)
-extern "C" int b200attn_debug_read_trace(unsigned long long* host_out, int count) {
-  unsigned int n = 0;
-  cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(n));
-  cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * count);
-  unsigned int zero = 0;
-  cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));
-  return (int)n;
-}
-#else
-#define TRACE(id) do {} while (0)
-#endif
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -245,7 +223,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   int seq_start = 0, len = p.seqlen, bcoord = b;
   if (p.cu_seqlens) {
     seq_start = p.cu_seqlens[b];
-    len = p.cu_seqlens[b + 1] - seq_start;
+    // a sequence longer than the max_seqlen the grid was sized for is cut there
+    len = min(p.cu_seqlens[b + 1] - seq_start, p.n_pairs * kPairM);
     bcoord = 0;
   }
   const int q0 = pair * kPairM;
@@ -394,7 +373,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           const int bh2 = grp2 * kHeadGroup + in2 % gh2;
           const int h2 = bh2 % p.heads_q, b2 = bh2 / p.heads_q;
           int ss2 = 0, len2 = p.seqlen, bc2 = b2;
-          if (p.cu_seqlens) { ss2 = p.cu_seqlens[b2]; len2 = p.cu_seqlens[b2 + 1] - ss2; bc2 = 0; }
+          if (p.cu_seqlens) { ss2 = p.cu_seqlens[b2]; len2 = min(p.cu_seqlens[b2 + 1] - ss2, p.n_pairs * kPairM); bc2 = 0; }
           const int q02 = pair2 * kPairM;
           if (q02 < len2) {
             const TileSeq seq2 = make_seq<BN>(p, q02, len2);
@@ -457,7 +436,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
       // every issued copy must have landed before the CTA may exit
       for (int c = max(cnt - NSTAGE, 0); c < cnt; ++c)
-        mbar_wait(kv_full(c % NSTAGE), (c / NSTAGE) & 1, abort_flag);
+        if (!mbar_wait(kv_full(c % NSTAGE), (c / NSTAGE) & 1, abort_flag)) mbar_drain(kv_full(c % NSTAGE), (c / NSTAGE) & 1);
     }
     } else if (warp == kMmaWarp) {
     // ================================================================= MMA
@@ -490,16 +469,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         else
           mma_ss_x4(tS(t), (uint32_t)da, (uint32_t)(da >> 32), (uint32_t)db, (uint32_t)(db >> 32), kIdescQK, issue);
         mma_commit(s_full(t), issue);
-        if (issue) TRACE(25 + t);
       };
       auto issue_pv = [&](int t, int s) {
         mbar_wait(p_full(t), pv_cnt[t] & 1, abort_flag);
         tc_fence_after();
-        if (issue) TRACE(10 + t);
         const uint64_t db = dv0 + (uint64_t)((s * L::kStageBytes) >> 4);
         mma_ts_x8(tO(t), tS(t), (uint32_t)db, (uint32_t)(db >> 32), kIdescPV, pv_cnt[t] > 0 ? 1u : 0u, issue);
         mma_commit(o_full(t), issue);
-        if (issue) TRACE(20 + t);
         ++pv_cnt[t];
       };
       if (!blk) {
@@ -510,6 +486,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (n_steps > 0) mma_commit(kv_empty(sK), issue);
         for (int j = 0; j < n_steps; ++j) {
           const int sV = wait_stage();
+          // Rows of the V tile past the sequence end belong to the next packed sequence (or to
+          // nobody): P is 0 there, but 0 * Inf/NaN would still poison O, so they are cleared
+          // like the reference's zero-padded loads (flash_attn_triton.py:155-165).
+          if (seq.kv(j) * BN + BN > len)
+            zero_tile_rows(smem_gen + 2 * L::kQBytes + sV * L::kStageBytes, kPanels, L::kKvPanel,
+                           max(len - seq.kv(j) * BN, 0), BN, lane);
           const bool more = j + 1 < n_steps;
           int sKn = 0;
           for (int t = 0; t < 2; ++t) {
@@ -529,7 +511,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int j = 0; j < n_steps; ++j) {
           for (int t = 0; t < 2; ++t) {
             const int ns = t ? ns1 : ns0;
-            if (j < ns) { const int s = wait_stage(); issue_pv(t, s); mma_commit(kv_empty(s), issue); }
+            if (j < ns) {
+              const int s = wait_stage();
+              // (rows past the sequence end inside the last KV block are cleared, see above)
+              for (int bx = 0; bx < 2; ++bx) {
+                const int u = ulist(t, min(2 * j + bx, n_u[t] - 1));
+                if ((u + 1) * kBlk > len)
+                  zero_tile_rows(smem_gen + 2 * L::kQBytes + s * L::kStageBytes, kPanels, L::kKvPanel,
+                                 kBlk * bx + max(len - u * kBlk, 0), kBlk * (bx + 1), lane);
+              }
+              issue_pv(t, s);
+              mma_commit(kv_empty(s), issue);
+            }
             if (j + 1 < ns) { const int s = wait_stage(); issue_qk(t, s); mma_commit(kv_empty(s), issue); }
           }
         }
@@ -554,12 +547,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (!step_active(t, j)) continue;
         mbar_wait(s_full(t), items & 1, abort_flag);
         tc_fence_after();
-        if (row == 0) TRACE(30 + t);
         uint32_t sr[BN];
 #pragma unroll
         for (int cc = 0; cc < BN / 32; ++cc) tmem_ld32(tS(t) + lane_off + 32 * cc, &sr[32 * cc]);
         tmem_wait_ld();
-        if (row == 0) TRACE(40 + t);
         bool vis0 = true, vis1 = true;   // does this warp's query block see each 64-column half?
         if (blk) {
           // columns [0,64) belong to KV block u0, [64,128) to u1; a row sees a
@@ -638,7 +629,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             tmem_st32(tO(t) + lane_off + 32 * cc, orr);
           }
         }
-        if (row == 0) TRACE(50 + t);
         const float mc = (m_use == -INFINITY) ? 0.f : m_use * c;
         float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
         uint32_t pr[BN / 2];
@@ -671,13 +661,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           }
         }
         sum0 += sum2; sum1 += sum3;
-        if (row == 0) TRACE(60 + t);
 #pragma unroll
         for (int cc = 0; cc < BN / 64; ++cc) tmem_st32(tS(t) + lane_off + 32 * cc, &pr[32 * cc]);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(p_full(t));
-        if (row == 0) TRACE(70 + t);
         l_run = l_run * alpha + (sum0 + sum1);
         m_run = m_use;
         ++items;
@@ -818,13 +806,16 @@ static int launch_prefill(const b200attn_prefill_args* a, const PrefillParams& p
     return B200ATTN_ERR_CUDA;
   auto kern = p.block_idx ? prefill_kernel<T, DP, BN, NSTAGE, true> : prefill_kernel<T, DP, BN, NSTAGE, false>;
   // the register count is a property of the binary: checked once per instantiation and mode
-  static bool regs_ok[2] = {false, false};
-  if (!regs_ok[p.block_idx ? 1 : 0]) {
+  static std::once_flag regs_once[2];
+  static int regs_status[2];
+  const int mode = p.block_idx ? 1 : 0;
+  std::call_once(regs_once[mode], [kern, mode] {
     cudaFuncAttributes fa;
-    if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return B200ATTN_ERR_CUDA;
-    if (fa.numRegs < kLaunchRegs) return B200ATTN_ERR_CUDA;  // register hand-over would not balance
-    regs_ok[p.block_idx ? 1 : 0] = true;
-  }
+    regs_status[mode] = (cudaFuncGetAttributes(&fa, kern) == cudaSuccess && fa.numRegs >= kLaunchRegs)
+                            ? B200ATTN_OK
+                            : B200ATTN_ERR_CUDA;   // fewer registers: the hand-over would not balance
+  });
+  if (regs_status[mode] != B200ATTN_OK) return regs_status[mode];
   // the shared-memory opt-in is per device: set on every call (a process may drive several GPUs)
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
     return B200ATTN_ERR_CUDA;
@@ -849,14 +840,13 @@ int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream
   const int maxlen = a->cu_seqlens ? a->max_seqlen : a->seqlen;
   p.n_pairs = (maxlen + kPairM - 1) / kPairM;
   {
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-      return B200ATTN_ERR_CUDA;
+    const DeviceInfo* di = nullptr;
+    st = device_info(&di);
+    if (st != B200ATTN_OK) return st;
 #ifndef B200ATTN_PREFETCH_WAVES
 #define B200ATTN_PREFETCH_WAVES 1
 #endif
-    p.prefetch_ahead = sms * B200ATTN_PREFETCH_WAVES;   // one CTA per SM
+    p.prefetch_ahead = di->sm_count * B200ATTN_PREFETCH_WAVES;   // one CTA per SM
   }
   const bool window = sparse && a->sparsity == B200ATTN_WINDOW;
   p.causal = window ? 1 : (a->causal ? 1 : 0);

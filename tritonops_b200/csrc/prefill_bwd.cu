@@ -62,24 +62,6 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
-#ifdef B200ATTN_TRACE
-// Debug builds only: (event id, SM clock) of one CTA, one slice per warp.
-constexpr int kBwdTraceSlice = 4096;
-__device__ unsigned long long g_bwd_trace[10 * kBwdTraceSlice];
-__device__ __forceinline__ void bwd_trace_ev(int id, unsigned& n) {
-  if (blockIdx.x != 0 || blockIdx.y != 3 || blockIdx.z != 1) return;   // a CTA with the longest walk
-  long long c;
-  asm volatile("mov.u64 %0, %%clock64;" : "=l"(c)::"memory");
-  if (n < kBwdTraceSlice)
-    g_bwd_trace[(threadIdx.x >> 5) * kBwdTraceSlice + n] = ((unsigned long long)id << 48) | ((unsigned long long)c & 0xffffffffffffULL);
-  ++n;
-}
-#define BTRACE(id) bwd_trace_ev(id, trace_n)
-#define BTRACE_DECL unsigned trace_n = 0
-#else
-#define BTRACE(id) do {} while (0)
-#define BTRACE_DECL do {} while (0)
-#endif
 
 template <int DP>
 struct BwdSmem {
@@ -117,7 +99,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
   int seq_start = 0, len = p.seqlen, bcoord = b;
   if (p.cu_seqlens) {
     seq_start = p.cu_seqlens[b];
-    len = p.cu_seqlens[b + 1] - seq_start;
+    // a sequence longer than the max_seqlen the grid was sized for is cut there
+    len = min(p.cu_seqlens[b + 1] - seq_start, p.n_kvtiles * kT);
     bcoord = 0;
   }
   const int kv0 = jt * kT;
@@ -135,8 +118,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kBarOffset + L::kNumBars * 8 + 4);
 
-  const int warp = threadIdx.x >> 5;
-  BTRACE_DECL;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar_kv, 1);
@@ -187,7 +169,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         int i, hq;
         pair_of(it, i, hq);
         if (it > 0) mbar_wait(bar_dv, (it - 1) & 1, abort_flag);
-        BTRACE(20);
         mbar_expect_tx(bar_do, L::kOperand);
         for (int pn = 0; pn < kPanels; ++pn)
           tma_load_4d(sbase + L::kDO + pn * L::kPanel, &tmap_do, bar_do, 64 * pn, seq_start + i * kT, hq, bcoord);
@@ -227,16 +208,23 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       pair_of(it, i, hq);
       const uint32_t q_off = (it & 1) ? L::kQ1 : L::kQ;
       const uint64_t d_q_mn = smem_desc_sw128(sbase + q_off, L::kPanel, 1024);
+      // Operand rows past the sequence end belong to the next packed sequence (or to nobody).
+      // P and dS are exact zeros there, but 0 * Inf/NaN would still poison the sums they are
+      // contracted over (K rows feed dQ; Q and dO rows feed dK and dV), so those rows are
+      // cleared, like the reference's zero-padded loads (flash_attn_triton.py:155-165).
+      const bool q_ragged = (i + 1) * kT > len;
       if (it == 0) {
         mbar_wait(bar_kv, 0, abort_flag);
         mbar_wait(bar_q0, 0, abort_flag);
+        if (kv0 + kT > len) zero_tile_rows(sgen + L::kK, kPanels, L::kPanel, len - kv0, kT, lane);
+        if (q_ragged) zero_tile_rows(sgen + L::kQ, kPanels, L::kPanel, max(len - i * kT, 0), kT, lane);
         tc_fence_after();
         issue_s(0);
       }
       // (S of later pairs is issued at the end of the pair before, behind its dQ product)
       mbar_wait(bar_do, it & 1, abort_flag);
+      if (q_ragged) zero_tile_rows(sgen + L::kDO, kPanels, L::kPanel, max(len - i * kT, 0), kT, lane);
       tc_fence_after();
-      if (issue) BTRACE(3);
       // dP = dO V^T
 #pragma unroll
       for (int ks = 0; ks < DP / 16; ++ks) {
@@ -248,11 +236,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       if (issue) bulk_wait_read_but_one();
       __syncwarp();
       mma_commit(bar_sdp, issue);
-      if (issue) BTRACE(4);
       // wait for P and dS in shared memory
       mbar_wait(bar_pds, it & 1, abort_flag);
       tc_fence_after();
-      if (issue) BTRACE(5);
       // The Q buffer of pair it - 1 held the second half of its dQ tile; once that is
       // read it takes the query tile of pair it + 1 (in L2 by now).
       if (it > 0 && it + 1 < n_iter) {
@@ -286,11 +272,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         mma_ss(tDP, d_ds_k + offa, d_k_mn + offb, kIdDQ, ks > 0, issue);   // dQ takes the dP columns
       }
       mma_commit(bar_dq, issue);
-      if (issue) BTRACE(6);
       // the S columns were read before P and dS were written: start the next pair's scores
       // now, so they are computed while this pair's dQ tile is being moved out
       if (it + 1 < n_iter) {
         mbar_wait(bar_q0 + 8 * ((it + 1) & 1), ((it + 1) >> 1) & 1, abort_flag);
+        int in, hqn;
+        pair_of(it + 1, in, hqn);
+        if ((in + 1) * kT > len)
+          zero_tile_rows(sgen + (((it + 1) & 1) ? L::kQ1 : L::kQ), kPanels, L::kPanel, max(len - in * kT, 0), kT, lane);
         tc_fence_after();
         issue_s(it + 1);
       }
@@ -299,7 +288,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       // fp32 accumulator in global memory, one bulk group each.  Rows past the sequence
       // end hold exact zeros.
       mbar_wait(bar_free, it & 1, abort_flag);
-      if (issue) BTRACE(2);
       if (issue) {
         const int tl0 = (p.cu_seqlens ? seq_start : b * p.seqlen) + i * kT;
         for (int pn = 0; pn < DP / 64; ++pn)
@@ -337,10 +325,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         const long long tl = p.cu_seqlens ? tok : (long long)b * p.seqlen + qi;
         dsum = p.dvec[tl * p.heads_q + hq];
       }
-      if (threadIdx.x == 0) BTRACE(10);
       mbar_wait(bar_sdp, it & 1, abort_flag);
       tc_fence_after();
-      if (threadIdx.x == 0) BTRACE(11);
       // visible keys of this row inside the tile: columns [0, lim)
       int lim = live ? min(kT, len - kv0) : 0;
       if (p.causal) lim = min(lim, qi - kv0 + 1);
@@ -379,11 +365,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       fence_proxy_async();       // generic-proxy writes -> visible to the tensor core's reads
       tc_fence_before();
       mbar_arrive(bar_pds);
-      if (threadIdx.x == 0) BTRACE(12);
       // dQ tile of this pair -> fp32 accumulator
       mbar_wait(bar_dq, it & 1, abort_flag);
       tc_fence_after();
-      if (threadIdx.x == 0) BTRACE(13);
       // scaled fp32 tile -> shared memory in the copy engine's 128-byte-swizzled layout
       // (one panel per 32 columns); the control warp adds it to global memory
       uint8_t* sStage = sgen + (half == 0 ? L::kP : ((it & 1) ? L::kQ1 : L::kQ));
@@ -404,7 +388,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar_free);
-      if (threadIdx.x == 0) BTRACE(14);
     }
     // ---- dK, dV of this key tile (every product has completed: the last bar_dq was waited)
     // (tcgen05.ld is warp-collective: every thread runs the loads, only the
@@ -449,18 +432,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
   }
 }
 
-#ifdef B200ATTN_TRACE
-}  // namespace
-}  // namespace b200attn
-extern "C" int b200attn_debug_read_bwd_trace(unsigned long long* host_out, int count) {
-  cudaMemcpyFromSymbol(host_out, b200attn::g_bwd_trace, sizeof(unsigned long long) * count);
-  static unsigned long long zeros[10 * b200attn::kBwdTraceSlice];
-  cudaMemcpyToSymbol(b200attn::g_bwd_trace, zeros, sizeof(zeros));
-  return count;
-}
-namespace b200attn {
-namespace {
-#endif
 
 // D[t, h] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head).
 template <typename T>
@@ -641,6 +612,8 @@ int prefill_bwd(const b200attn_prefill_bwd_args* a, cudaStream_t stream) {
   const size_t need = prefill_bwd_workspace_bytes(a);
   if (!a->workspace || a->workspace_bytes < need) return B200ATTN_ERR_WORKSPACE;
   if ((uintptr_t)a->workspace & 15) return B200ATTN_ERR_ALIGN;
+  st = device_info(nullptr);
+  if (st != B200ATTN_OK) return st;
   const long long rows = total_rows(a);
   const int DP = dpad(a->head_dim);
   BwdParams p;

@@ -342,6 +342,7 @@ int rmsnorm_fwd(const b200attn_rmsnorm_fwd_args* a, cudaStream_t stream) {
   if (a->rows < 0 || a->dim <= 0 || a->x_stride_row < a->dim || a->y_stride_row < a->dim) return B200ATTN_ERR_SHAPE;
   if (((uintptr_t)a->x | (uintptr_t)a->y) & (elem_size(a->x_dtype) - 1)) return B200ATTN_ERR_ALIGN;
   if (a->rows == 0) { set_launch_count(0); return B200ATTN_OK; }
+  if (int dst = device_info(nullptr)) return dst;
   const bool wf = a->w_dtype == B200ATTN_F32;
   switch (a->x_dtype) {
     case B200ATTN_F32: return launch_fwd<float, float>(a, stream);
@@ -363,6 +364,7 @@ int rmsnorm_bwd(const b200attn_rmsnorm_bwd_args* a, cudaStream_t stream) {
   if (a->dim > kBwdThreadsRms * kBwdMaxCols) return B200ATTN_ERR_TOO_LARGE;
   if (!a->workspace || a->workspace_bytes < rmsnorm_bwd_workspace_bytes(a)) return B200ATTN_ERR_WORKSPACE;
   if ((uintptr_t)a->workspace & 3) return B200ATTN_ERR_ALIGN;
+  if (int dst = device_info(nullptr)) return dst;
   const bool wf = a->w_dtype == B200ATTN_F32;
   switch (a->x_dtype) {
     case B200ATTN_F32: return launch_bwd_rms<float, float>(a, stream);

@@ -35,6 +35,7 @@ int selftest_bounded_wait(int32_t* status_word, long long budget_cycles, long lo
   if (!status_word) return B200ATTN_ERR_NULL;
   // the probe is meant to give up quickly: refuse budgets beyond ~50 ms
   if (budget_cycles <= 0 || budget_cycles > 100000000LL) return B200ATTN_ERR_SHAPE;
+  if (int dst = device_info(nullptr)) return dst;
   bounded_wait_probe_kernel<<<1, 32, 0, stream>>>(status_word, budget_cycles, waited_cycles);
   set_launch_count(1);
   return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;

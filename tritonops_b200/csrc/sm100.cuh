@@ -80,6 +80,34 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return mbar_wait_for(bar, parity, abort_flag, kWaitBudgetCycles);
 }
 
+// Wait, with a budget of its own, for a copy this CTA issued itself: used on the way out after
+// a wait has given up (the abort flag is up, so mbar_wait would return at once), because a CTA
+// must not exit while bulk copies into its shared memory are still in flight.
+constexpr long long kDrainBudgetCycles = 400000000LL;   // ~0.2 s
+__device__ __forceinline__ bool mbar_drain(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int polls = 0;
+  while (!mbar_try_wait(bar, parity))
+    if ((++polls & 255) == 0 && clock64() - t0 > kDrainBudgetCycles) return false;
+  return true;
+}
+
+// Clear rows [row0, row1) of a 16-bit operand tile laid out as `panels` 64-column panels of
+// 128-byte rows (`panel_bytes` apart), by the 32 lanes of one warp.  The 128-byte swizzle only
+// permutes 16-byte chunks inside a row, so whole rows can be cleared without knowing it.  Ends
+// with the fence that orders these generic-proxy stores before the tensor core's reads.
+__device__ __forceinline__ void zero_tile_rows(uint8_t* tile, int panels, int panel_bytes, int row0, int row1,
+                                               int lane) {
+  const int per_row = panels * 8;
+  for (int i = lane; i < (row1 - row0) * per_row; i += 32) {
+    const int r = row0 + i / per_row, c = i % per_row;
+    *reinterpret_cast<uint4*>(tile + (c >> 3) * panel_bytes + r * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+}
+
 // ----------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -33,14 +33,20 @@ class HostPrefill:
         self.slots: List[_Slot] = [_Slot() for _ in range(n_slots)]
 
     def _stage(self, slot: _Slot, n: int, hq, hk, hv):
+        """Make the slot's staging tensors hold n tokens.  Called once per slot at the start of
+        run(), sized for the longest sequence of that call, so nothing is reallocated while the
+        pipeline is running.  Old tensors may still be read by a kernel of an earlier run() on
+        s_run: s_in waits for that kernel before they are dropped (their memory goes back to
+        s_in's pool and could otherwise be handed out and overwritten at once)."""
         if slot.cap < n or slot.q is None or slot.q.shape[2:] != hq.shape[2:] or slot.k.shape[2:] != hk.shape[2:] \
                 or slot.q.dtype != hq.dtype:
             with torch.cuda.stream(self.s_in):
+                if slot.inputs_free is not None:
+                    self.s_in.wait_event(slot.inputs_free)
                 slot.q = torch.empty(1, n, *hq.shape[2:], device=self.dev, dtype=hq.dtype)
                 slot.k = torch.empty(1, n, *hk.shape[2:], device=self.dev, dtype=hk.dtype)
                 slot.v = torch.empty(1, n, *hv.shape[2:], device=self.dev, dtype=hv.dtype)
             slot.cap = n
-            slot.inputs_free = None
 
     def run(self, hq, hk, hv, cu_seqlens: Sequence[int], ho, hl, *, scale: float, scale_has_log2e: bool = False,
             causal: bool = True, lse_base2: bool = False) -> None:
@@ -56,13 +62,16 @@ class HostPrefill:
         for s in (self.s_in, self.s_run, self.s_out):
             s.wait_event(start)
         cu = [int(x) for x in cu_seqlens]
+        longest = max([cu[b + 1] - cu[b] for b in range(len(cu) - 1)] + [0])
+        if longest > 0:
+            for slot in self.slots:
+                self._stage(slot, max(longest, slot.cap), hq, hk, hv)
         for b in range(len(cu) - 1):
             s0, s1 = cu[b], cu[b + 1]
             n = s1 - s0
             if n <= 0:
                 continue
             slot = self.slots[b % len(self.slots)]
-            self._stage(slot, max(n, slot.cap), hq, hk, hv)
             with torch.cuda.stream(self.s_in):
                 if slot.inputs_free is not None:
                     self.s_in.wait_event(slot.inputs_free)

@@ -6,6 +6,7 @@ exists: CPU tensors are rejected."""
 import ctypes as C
 import math
 import os
+import threading
 from typing import Optional, Tuple
 
 import torch
@@ -23,18 +24,32 @@ _DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
 launch_counter = 0
 
 
-# Debug mode (B200ATTN_DEBUG_STATUS=1): the prefill kernels get a status word and every call is
-# followed by a stream synchronisation and a check of it, so a bounded device-side wait that gave
-# up surfaces as an exception at the call that caused it.  Off by default (it costs a host sync).
+# Debug mode (B200ATTN_DEBUG_STATUS=1): the prefill and decoding kernels get a status word and
+# every call is followed by a stream synchronisation and a check of it, so a bounded device-side
+# wait that gave up surfaces as an exception at the call that caused it.  Off by default (it costs
+# a host sync).
 DEBUG_STATUS = os.environ.get("B200ATTN_DEBUG_STATUS", "0") == "1"
 _status_words = {}
+_status_lock = threading.Lock()
 
 
 def _status_word(dev) -> Tensor:
     key = torch.device(dev).index
-    if key not in _status_words:
-        _status_words[key] = torch.zeros(1, device=dev, dtype=torch.int32)
-    return _status_words[key]
+    if key is None:
+        key = torch.cuda.current_device()
+    with _status_lock:      # calls may come from several host threads
+        if key not in _status_words:
+            _status_words[key] = torch.zeros(1, device=torch.device("cuda", key), dtype=torch.int32)
+        return _status_words[key]
+
+
+def _same_head_dim(q: Tensor, *others: Tensor):
+    """One head_dim for Q, K, V (and O): the kernels take a single value.  The reference wrappers
+    accept a narrower V (flash_attn_decoding.py:233-236) but allocate O with Q's width
+    (flash_attn_triton.py:608), so only equal widths ever worked there either."""
+    for t in others:
+        if t.shape[-1] != q.shape[-1]:
+            raise ValueError(f"b200attn: q, k and v must share head_dim (got {q.shape[-1]} and {t.shape[-1]})")
 
 
 def _check_status(dev, what: str):
@@ -107,6 +122,7 @@ def _decode_op_impl(q: Tensor, k: Tensor, v: Tensor, lens: Tensor, lens_are_cu: 
                scale: float, chunk: int, sparsity: int, window_global: int, window_local: int,
                block_idx: Optional[Tensor], block_cnt: Optional[Tensor],
                block_size: int) -> Tensor:
+    _same_head_dim(q, k, v)
     _need_cuda(q, k, v, lens, block_idx, block_cnt)
     if q.dtype not in _DT or k.dtype != q.dtype or v.dtype != q.dtype:
         raise ValueError("b200attn: q, k, v must share dtype float16 or bfloat16")
@@ -137,7 +153,10 @@ def _decode_op_impl(q: Tensor, k: Tensor, v: Tensor, lens: Tensor, lens_are_cu: 
     a.workspace, a.workspace_bytes = _ptr(ws), ws.numel()
     fn = L.b200attn_decode_fwd if sparsity == DENSE else L.b200attn_sparse_decode_fwd
     with torch.cuda.device(q.device):
+        if DEBUG_STATUS:
+            a.status_word = _ptr(_status_word(q.device))
         _lib.check(fn(C.byref(a), _stream(q)))
+        _check_status(q.device, "decoding")
     _count()
     return o
 
@@ -173,6 +192,7 @@ def paged_decode(q: Tensor, k_pages: Tensor, v_pages: Tensor, page_table: Tensor
                  max_seqlen: Optional[int] = None, scale: Optional[float] = None, chunk: int = 0) -> Tensor:
     """Split-KV GQA decoding over page pools [num_pages, page_size, Hkv, D] addressed through
     page_table int32 [B, max_pages]; see b200attn_paged_decode_fwd in include/b200attn.h."""
+    _same_head_dim(q, k_pages, v_pages)
     _need_cuda(q, k_pages, v_pages, page_table, seqlens)
     if q.dtype not in _DT or k_pages.dtype != q.dtype or v_pages.dtype != q.dtype:
         raise ValueError("b200attn: q, k, v must share dtype float16 or bfloat16")
@@ -198,7 +218,10 @@ def paged_decode(q: Tensor, k_pages: Tensor, v_pages: Tensor, page_table: Tensor
     ws = torch.empty(max(need, 16), device=q.device, dtype=torch.uint8)
     a.workspace, a.workspace_bytes = _ptr(ws), ws.numel()
     with torch.cuda.device(q.device):
+        if DEBUG_STATUS:
+            a.status_word = _ptr(_status_word(q.device))
         _lib.check(L.b200attn_paged_decode_fwd(C.byref(a), _stream(q)))
+        _check_status(q.device, "paged decoding")
     _count()
     return o
 
@@ -277,6 +300,7 @@ def _prefill_op_impl(q: Tensor, k: Tensor, v: Tensor, cu_seqlens: Optional[Tenso
                 scale: float, scale_has_log2e: bool, causal: bool, lse_base2: bool, sparsity: int,
                 window_local: int, window_global: int, block_idx: Optional[Tensor],
                 block_cnt: Optional[Tensor], block_size: int) -> Tuple[Tensor, Tensor]:
+    _same_head_dim(q, k, v)
     _need_cuda(q, k, v, cu_seqlens, block_idx, block_cnt)
     if q.dtype not in _DT or k.dtype != q.dtype or v.dtype != q.dtype:
         raise ValueError("b200attn: q, k, v must share dtype float16 or bfloat16")
@@ -356,6 +380,7 @@ def prefill(q, k, v, *, cu_seqlens=None, max_seqlen=None, scale=None, scale_has_
 def _prefill_bwd_op_impl(q: Tensor, k: Tensor, v: Tensor, o: Tensor, d_o: Tensor, lse: Tensor,
                     cu_seqlens: Optional[Tensor], max_seqlen: int, scale: float,
                     scale_has_log2e: bool, causal: bool, lse_base2: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    _same_head_dim(q, k, v, o, d_o)
     _need_cuda(q, k, v, o, d_o, lse, cu_seqlens)
     if q.dtype not in _DT or any(t.dtype != q.dtype for t in (k, v, o, d_o)):
         raise ValueError("b200attn: q, k, v, o, do must share dtype float16 or bfloat16")
