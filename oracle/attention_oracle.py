@@ -507,3 +507,49 @@ def paged_to_padded(pages, page_table, seqlens, capacity=None):
             t1 = min(n, t0 + page)
             out[b, t0:t1] = pages[int(page_table[b, i]), :t1 - t0]
     return out
+
+
+# --------------------------------------------------------------------------
+# CPU-baseline forms of the block-index layouts: the reference's naive torch
+# loops with the mask / gather of the block lists in place of its windows
+# --------------------------------------------------------------------------
+def block_sparse_prefill_refpath(q, k, v, cu_seqlens, block_idx, block_cnt, *, block=64, heads=None):
+    """The dense masked per-(b, h) loop of flash_attn_sparse_torch
+    (flash_attn_sparse_attn_triton.py:391-442) with the mask expanded from a block list instead
+    of the two windows: scores, mask, scale and softmax all in the input dtype.  `heads` limits
+    the loop to some (b, h) pairs (the CPU baseline times a stated subset)."""
+    _, T, H, Dq = q.shape
+    g = H // k.shape[-2]
+    o = torch.zeros_like(q)
+    softmax_scale = Dq ** -0.5
+    for b, (s0, s1) in enumerate(_lens(cu_seqlens)):
+        n = s1 - s0
+        for h in range(H):
+            if heads is not None and (b, h) not in heads:
+                continue
+            mask = block_list_mask(n, block, block_idx[b, h], block_cnt[b, h], True)
+            bq, bk, bv = q[0, s0:s1, h], k[0, s0:s1, h // g], v[0, s0:s1, h // g]
+            qk = bq @ bk.T
+            qk = torch.where(mask, qk, torch.full_like(qk, -math.inf)) * softmax_scale
+            o[0, s0:s1, h] = qk.softmax(dim=-1) @ bv
+    return o
+
+
+def block_sparse_decoding_refpath(q, k_cache, v_cache, block_idx, *, block=64):
+    """Gather the listed blocks of each (b, KV head), then the math of the sparse
+    flash_attn_decoding_torch (flash_attn_decoding_sparse.py:368-406) with every gathered key
+    visible: scores, softmax and P V in the input dtype.  Lists are full (no -1 padding)."""
+    B, Hq, D = q.shape
+    Hkv = k_cache.shape[2]
+    g = Hq // Hkv
+    o = torch.zeros(B, Hq, v_cache.shape[3], dtype=q.dtype)
+    qk_scale = D ** -0.5
+    off = torch.arange(block)
+    for b in range(B):
+        for hk in range(Hkv):
+            tok = (block_idx[b, hk].long()[:, None] * block + off[None, :]).reshape(-1)
+            bk, bv = k_cache[b, tok, hk], v_cache[b, tok, hk]
+            bq = q[b, hk * g:(hk + 1) * g]
+            qk = torch.einsum("hd,kd->hk", bq, bk).to(q.dtype) * qk_scale
+            o[b, hk * g:(hk + 1) * g] = torch.einsum("hk,kd->hd", qk.softmax(dim=-1).to(q.dtype), bv)
+    return o

@@ -90,3 +90,111 @@ def decoding(q, kc, vc, cu):
 def sparse_decoding(q, kc, vc, cu, glob, local):
     """flash_attention_sparse_decoding (flash_attn_decoding_sparse.py:222-365)."""
     return load()[2].flash_attention_sparse_decoding(q, kc, vc, cu, global_window_size=glob, local_window_size=local)
+
+
+# --------------------------------------------------------------------------
+# timing of the reference's kernels (bench.py runs this file as a child process)
+# --------------------------------------------------------------------------
+def _events_ms(fn, steps, warmup):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def bench_on_gpu():
+    """Config 2 (kernel alone after its autotune, and through the reference's wrapper with its
+    allocations, memsets and .item() synchronisation), config 3 through its wrapper, and the
+    window kernel on the reference test's shape (flash_attn_sparse_attn_triton.py:445-503).  One
+    JSON line; a kernel that does not run here is reported by its exception text."""
+    import json
+    import sys
+    import torch
+    sys.path.insert(0, os.path.dirname(HERE))
+    from tritonops_b200 import workloads
+    dev = torch.device("cuda", 0)
+    out = {"what": "the reference's Triton kernels (triton %s) on this GPU, CUDA events" % __import__("triton").__version__}
+    try:
+        w = workloads.dense_causal(4, 32, 4096, 128, 1, dev, name="cfg2")
+        o = torch.zeros_like(w.q)
+        lse = torch.zeros(w.q.shape[:3], device=dev, dtype=torch.float32)
+        dense_prefill_kernel_only(w.q, w.k, w.v, w.cu_seqlens, o, lse, 4096)      # compiles and autotunes
+        out["cfg2_kernel_ms"] = _events_ms(lambda: dense_prefill_kernel_only(w.q, w.k, w.v, w.cu_seqlens, o, lse, 4096), 20, 3)
+        out["cfg2_kernel_tflops"] = w.flops / out["cfg2_kernel_ms"] / 1e9
+        out["cfg2_wrapper_ms"] = _events_ms(lambda: dense_prefill(w.q, w.k, w.v, w.cu_seqlens), 10, 3)
+        try:
+            out["cfg2_autotune_choice"] = str(load()[0].flash_attn_fwd_kernel.best_config)
+        except Exception:
+            pass
+        del w, o, lse
+    except Exception as e:  # noqa: BLE001
+        out["cfg2_error"] = f"{type(e).__name__}: {str(e)[:300]}"
+    try:
+        w3 = workloads.cfg3(dev)
+        decoding(w3.q, w3.k_cache, w3.v_cache, w3.cu_seqlens)
+        out["cfg3_wrapper_ms"] = _events_ms(lambda: decoding(w3.q, w3.k_cache, w3.v_cache, w3.cu_seqlens), 10, 3)
+        out["cfg3_wrapper_GBs"] = w3.kv_bytes / out["cfg3_wrapper_ms"] / 1e6
+        del w3
+    except Exception as e:  # noqa: BLE001
+        out["cfg3_error"] = f"{type(e).__name__}: {str(e)[:300]}"
+    try:
+        g = torch.Generator().manual_seed(42)
+        q, k, v = (torch.rand(1, 4 * 2048, 4, 96, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
+        cu = (torch.arange(5, dtype=torch.int32) * 2048).to(dev)
+        window_prefill(q, k, v, cu, 128, 0)
+        out["window_test_shape_ms"] = _events_ms(lambda: window_prefill(q, k, v, cu, 128, 0), 20, 3)
+    except Exception as e:  # noqa: BLE001
+        out["window_error"] = f"{type(e).__name__}: {str(e)[:300]}"
+    print(json.dumps(out))
+
+
+def interpret_cfg1():
+    """Config 1's inputs through the reference's dense kernel executed by Triton's CPU
+    interpreter (TRITON_INTERPRET=1 must be set before this process imports triton); the
+    autotuner needs a GPU driver, so the kernel is entered through its `.fn`."""
+    import json
+    import sys
+    import time
+    import torch
+    import triton
+    sys.path.insert(0, os.path.dirname(HERE))
+    from tritonops_b200 import workloads
+    assert os.environ.get("TRITON_INTERPRET") == "1"
+    dense = load()[0]
+    w = workloads.cfg1("cpu")
+    q, k, v, cu = w.q, w.k, w.v, w.cu_seqlens
+    _, T, hq, d = q.shape
+    o = torch.zeros_like(q)
+    lse = torch.zeros(1, T, hq, dtype=torch.float32)
+
+    def run():
+        dense.flash_attn_fwd_kernel.fn[(hq, 1, 1)](
+            q, k, v, o, cu, lse, q.stride(1), q.stride(2), q.stride(3), k.stride(1), k.stride(2), k.stride(3),
+            v.stride(1), v.stride(2), v.stride(3), o.stride(1), o.stride(2), o.stride(3), lse.stride(1), lse.stride(2),
+            BLOCK_SIZE_QD=triton.next_power_of_2(d), HEAD_DIM_Q=d, HEAD_DIM_V=d, BLOCK_SIZE_N=128, BLOCK_SIZE_KN=128,
+            BLOCK_SIZE_D=128, NUM_HEADS=hq, GQA_RATIO=1, sm_scale=d ** -0.5 * LOG2E)
+
+    run()
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < 2.0 and n < 50:
+        run()
+        n += 1
+    dt = time.perf_counter() - t0
+    print(json.dumps({"value": dt / n * 1e6, "unit": "us per call", "cores": 1, "kind": "reference",
+                      "sample": f"{n} calls of the reference's flash_attn_fwd_kernel (causal) under TRITON_INTERPRET=1 "
+                                f"on cfg1's inputs (fp16, B=1 H=2 S=128 D=64)"}))
+
+
+if __name__ == "__main__":
+    import sys as _sys
+    if "--bench" in _sys.argv:
+        bench_on_gpu()
+    elif "--interpret-cfg1" in _sys.argv:
+        interpret_cfg1()

@@ -47,3 +47,25 @@ def test_paged_to_padded_round_trip():
     assert pad.shape == (2, 48, 2, 8)
     assert torch.equal(pad[0, 16:32], pages[7]) and torch.equal(pad[0, 32:40], pages[1, :8])
     assert torch.equal(pad[1, 16:17], pages[0, :1]) and pad[1, 17:].abs().sum() == 0 and pad[0, 40:].abs().sum() == 0
+
+
+def test_block_list_cpu_baseline_forms_agree_with_fp32_math():
+    """The low-precision loops bench.py times as the CPU baseline of the block-list configs
+    compute the same attention as the fp32 oracle, to bf16 accuracy."""
+    from tritonops_b200 import workloads
+    g = torch.Generator().manual_seed(0)
+    n, H, D = 256, 2, 64
+    q, k, v = (torch.randn(1, n, H, D, generator=g).to(torch.bfloat16) for _ in range(3))
+    cu = torch.tensor([0, n], dtype=torch.int32)
+    idx, cnt = workloads.block_sparse_lists(1, H, n // 64, 2, 0.5, 1)
+    ref, _ = orc.block_sparse_prefill_exact(q, k, v, cu, idx, cnt)
+    low = orc.block_sparse_prefill_refpath(q, k, v, cu, idx, cnt)
+    assert (low.float() - ref).abs().max().item() <= 4e-2
+    only = orc.block_sparse_prefill_refpath(q, k, v, cu, idx, cnt, heads={(0, 1)})
+    assert torch.equal(only[0, :, 1], low[0, :, 1]) and only[0, :, 0].abs().max().item() == 0.0
+    qd = torch.randn(2, 4, D, generator=g).to(torch.bfloat16)
+    kc, vc = (torch.randn(2, 512, 2, D, generator=g).to(torch.bfloat16) for _ in range(2))
+    sel = workloads.topk_block_lists(2, 2, 8, 3, 4)
+    ref = orc.block_sparse_decoding_exact(qd, kc, vc, [512, 512], sel)
+    low = orc.block_sparse_decoding_refpath(qd, kc, vc, sel)
+    assert (low.float() - ref).abs().max().item() <= 4e-2

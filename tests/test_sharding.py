@@ -71,3 +71,51 @@ def test_two_rank_reduction_gloo():
         ret = mgr.dict()
         mp.spawn(_worker, args=(world, 29531, ret), nprocs=world, join=True)
         assert ret[0] == ret[1] == (11.0, 128.0)
+
+
+@pytest.mark.parametrize("B,Hkv,world", [(4, 32, 1), (4, 32, 2), (4, 32, 4), (4, 32, 8), (2, 16, 8), (3, 5, 4), (1, 2, 8)])
+def test_prefill_unit_pieces_tile_the_units(B, Hkv, world):
+    seen = []
+    for r in range(world):
+        for b0, b1, h0, h1 in sharding.prefill_unit_pieces(B, Hkv, world, r):
+            assert 0 <= b0 < b1 <= B and 0 <= h0 < h1 <= Hkv
+            assert (h0, h1) == (0, Hkv) or b1 == b0 + 1          # partial heads only inside one sequence
+            seen += [b * Hkv + h for b in range(b0, b1) for h in range(h0, h1)]
+    assert seen == list(range(B * Hkv))                           # disjoint, complete and in order
+
+
+def _shard_worker(rank, world, port, ret):
+    """Each rank attends over its own (sequence x KV head) rectangles (the CPU oracle stands in
+    for the kernel here); gathered and put back in place they must equal the unsharded result
+    bit for bit, because every (sequence, head) is computed independently."""
+    from oracle import attention_oracle as orc
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(0)
+        lens, Hq, Hkv, D = [70, 33, 128], 6, 3, 32
+        cu = [0, 70, 103, 231]
+        q = torch.randn(1, 231, Hq, D, generator=g).to(torch.bfloat16)
+        k = torch.randn(1, 231, Hkv, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(1, 231, Hkv, D, generator=g).to(torch.bfloat16)
+        mine = torch.zeros(1, 231, Hq, D, dtype=torch.bfloat16)
+        for piece in sharding.prefill_unit_pieces(len(lens), Hkv, world, rank):
+            qs, ks, vs, cus = sharding.slice_prefill_piece(q, k, v, cu, piece)
+            o = orc.dense_prefill_refpath(qs, ks, vs, torch.tensor(cus, dtype=torch.int32))
+            b0, b1, h0, h1 = piece
+            mine[:, cu[b0]:cu[b1], h0 * 2:h1 * 2] = o
+        bits = mine.view(torch.int16).to(torch.int32)       # disjoint pieces: a sum of bit patterns is a gather
+        dist.all_reduce(bits, op=dist.ReduceOp.SUM)
+        mine = bits.to(torch.int16).view(torch.bfloat16)
+        full = orc.dense_prefill_refpath(q, k, v, torch.tensor(cu, dtype=torch.int32))
+        ret[rank] = bool(torch.equal(mine, full))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_prefill_equals_unsharded_gloo():
+    world = 2
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_shard_worker, args=(world, 29537, ret), nprocs=world, join=True)
+        assert ret[0] is True and ret[1] is True

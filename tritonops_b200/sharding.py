@@ -38,6 +38,38 @@ def shard_prefill_heads(q, k, v, world: int, rank: int):
     return q[:, :, b * g:e * g], k[:, :, b:e], v[:, :, b:e]
 
 
+def prefill_unit_pieces(n_batch: int, n_kv_heads: int, world: int, rank: int) -> List[Tuple[int, int, int, int]]:
+    """The (sequence, KV head) units of a prefill, numbered b * n_kv_heads + hk (the order of the
+    reference grid's first axis, flash_attn_triton.py:83-91, taken per KV head so a query-head
+    group stays with its KV head), split into `world` contiguous slices.  Returns rank's slice as
+    rectangles (b0, b1, hk0, hk1): sequences b0..b1-1, KV heads hk0..hk1-1 -- at most three (the
+    head tail of a first sequence, whole sequences, the head prefix of a last one)."""
+    u0, u1 = contiguous_shard(n_batch * n_kv_heads, world, rank)
+    pieces: List[Tuple[int, int, int, int]] = []
+    while u0 < u1:
+        b, hk = divmod(u0, n_kv_heads)
+        if hk == 0 and u1 - u0 >= n_kv_heads:
+            nb = (u1 - u0) // n_kv_heads
+            pieces.append((b, b + nb, 0, n_kv_heads))
+            u0 += nb * n_kv_heads
+        else:
+            hk1 = min(n_kv_heads, hk + (u1 - u0))
+            pieces.append((b, b + 1, hk, hk1))
+            u0 += hk1 - hk
+    return pieces
+
+
+def slice_prefill_piece(q, k, v, cu_seqlens: Sequence[int], piece: Tuple[int, int, int, int]):
+    """Views of packed [1, T, H, D] prefill inputs for one rectangle of prefill_unit_pieces:
+    (q, k, v, cu) with cu (host integers) rebased to the first sequence of the piece.  No copy:
+    token rows are a contiguous range, heads a strided slice the kernels take as is."""
+    b0, b1, hk0, hk1 = piece
+    g = q.shape[2] // k.shape[2]
+    t0, t1 = int(cu_seqlens[b0]), int(cu_seqlens[b1])
+    cu = [int(cu_seqlens[b]) - t0 for b in range(b0, b1 + 1)]
+    return q[:, t0:t1, hk0 * g:hk1 * g], k[:, t0:t1, hk0:hk1], v[:, t0:t1, hk0:hk1], cu
+
+
 def max_over_ranks(value: float, device=None) -> float:
     """Max of a per-rank scalar (timings are reported as the slowest rank's)."""
     import torch.distributed as dist
