@@ -431,7 +431,7 @@ def run_ours(args, rank, world, local_rank, cpu_base):
     regions = []
     for _ in range(5):
         ms_r, win = region(step, args.steps, warmup=0)
-        regions.append({"ms_per_step": ms_r, "tflops": w.flops / ms_r / 1e9, "clocks": sampler.window(*win)})
+        regions.append({"ms_per_step": ms_r, "tflops": w.flops / ms_r / 1e9, "clocks": sampler.window(*win), "window": win})
     order = sorted(range(len(regions)), key=lambda i: regions[i]["ms_per_step"])
     med = regions[order[len(order) // 2]]
     ms = med["ms_per_step"]
@@ -729,18 +729,28 @@ def run_ours(args, rank, world, local_rank, cpu_base):
         guard("cfg1", do_cfg1)
 
     sampler.stop()
-    t_lo, t_hi = min(a for a, _ in windows), max(b for _, b in windows)
+    # `clocks` describes the headline's timed regions; the long region and the rest have their own record
+    head = [s for s in sampler.samples if any(r["window"][0] <= s[0] <= r["window"][1] for r in regions)]
+    clocks = dict(med["clocks"])
+    if head:
+        mhz = sorted(s[1] for s in head)
+        bits = 0
+        for s in head:
+            bits |= s[2]
+        clocks.update(sm_mhz=mhz[len(mhz) // 2], samples=len(head), power_w_max=max(s[3] for s in head),
+                      reasons=[n for n, b in ClockSampler.REASONS if bits & b])
+    clocks["what"] = "NVML samples inside the five headline regions; the sustained region has its own record"
     busy = [s for s in sampler.samples if any(a <= s[0] <= b for a, b in windows)]
-    clocks = sampler.window(t_lo, t_hi)
     if busy:
         mhz = sorted(s[1] for s in busy)
         bits = 0
         for s in busy:
             bits |= s[2]
-        clocks.update(sm_mhz=mhz[len(mhz) // 2], samples=len(busy),
-                      reasons=[n for n, b in ClockSampler.REASONS if bits & b],
-                      power_w_max=max(s[3] for s in busy))
-    clocks["headline_region"] = med["clocks"]
+        clocks["all_timed_regions"] = {"sm_mhz": mhz[len(mhz) // 2], "sm_mhz_min": mhz[0], "samples": len(busy),
+                                       "power_w_max": max(s[3] for s in busy),
+                                       "reasons": [n for n, b in ClockSampler.REASONS if bits & b]}
+    for r in regions:
+        r.pop("window", None)
     torch.cuda.empty_cache()
 
     # ---------------- the reference's Triton kernels on this GPU (one GPU only; own process)
