@@ -1,9 +1,8 @@
 """Generate the golden fixtures under tests/golden/ by running the REFERENCE.
 
-Run in a container that has the reference checkout (default /root/reference,
-override with REFERENCE_ROOT):
+Run where a checkout of the reference exists, named by REFERENCE_ROOT:
 
-    python tests/golden/make_golden.py
+    REFERENCE_ROOT=<checkout of rookie-joe/TritonOps> python tests/golden/make_golden.py
 
 Inputs are the seeded recipes of cases.py; the fixtures hold the reference's
 outputs plus an input checksum.  Two files are written:
@@ -32,7 +31,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 from cases import build, checksum  # noqa: E402
 
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set REFERENCE_ROOT to a checkout of the reference (rookie-joe/TritonOps)")
 STORE = {}
 
 

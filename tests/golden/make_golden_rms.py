@@ -1,6 +1,6 @@
 """Generate tests/golden/golden_rms.npz by running the REFERENCE's RMSNorm.
 
-    python tests/golden/make_golden_rms.py        (needs the reference checkout, REFERENCE_ROOT or /root/reference)
+    REFERENCE_ROOT=<checkout of rookie-joe/TritonOps> python tests/golden/make_golden_rms.py
 
 Recorded per case of rms_cases.py: the output and the gradients of the reference's
 torch module (common/rms.py:385-427) on CPU fp32 tensors, and the output of its
@@ -20,7 +20,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 from rms_cases import EPS, SHAPES, build  # noqa: E402
 
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set REFERENCE_ROOT to a checkout of the reference (rookie-joe/TritonOps)")
 
 
 def torch_part():
