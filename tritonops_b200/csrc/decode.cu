@@ -403,15 +403,26 @@ decode_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     if (lane == 0) {
       prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
       int issued = 0;
+      // Block lists and page tables: the block holding a stage's first key is looked up one
+      // stage ahead (the load is in flight during the wait for the stage to become free), and
+      // boxes of the stage that lie in the same block reuse it.
+      const bool listed = km.mode >= 2;
+      int nxt_blk = (listed && n_tiles > 0) ? km.blocks[c_begin / km.bsize] : 0;
       for (int tile = 0; tile < n_tiles; ++tile, ++issued) {
         const int s = tile % L::kStages;
-        if (!mbar_wait(empty(s), ((tile / L::kStages) & 1) ^ 1, abort_flag)) break;
         const int v0 = c_begin + tile * kStageTok;
+        const int cur_blk = nxt_blk;
+        const int cur_idx = listed ? v0 / km.bsize : 0;
+        const int cur_off = listed ? v0 - cur_idx * km.bsize : 0;
+        if (listed && tile + 1 < n_tiles) nxt_blk = km.blocks[(v0 + kStageTok) / km.bsize];
+        if (!mbar_wait(empty(s), ((tile / L::kStages) & 1) ^ 1, abort_flag)) break;
         const int nbox = min(kStageTok / kBoxTok, (c_end - v0 + kBoxTok - 1) / kBoxTok);
         mbar_expect_tx(full(s), nbox * 2 * L::kPanels * kBoxTok * 128);
         const uint32_t kdst = sbase + s * L::kStageBytes, vdst = kdst + L::kTileBytes;
         for (int i = 0; i < nbox; ++i) {
-          const int tok = km.to_token(v0 + kBoxTok * i);   // 16 consecutive cache rows (rows past the end are masked)
+          // 16 consecutive cache rows (rows past the end are masked)
+          const int tok = (listed && cur_off + kBoxTok * i < km.bsize) ? cur_blk * km.bsize + cur_off + kBoxTok * i
+                                                                       : km.to_token(v0 + kBoxTok * i);
           for (int pn = 0; pn < L::kPanels; ++pn) {
             const uint32_t off = pn * L::kPanelBytes + i * kBoxTok * 128;
             tma_load_4d(kdst + off, &tmap_k, full(s), 64 * pn, tok, hk, map_b);
