@@ -50,7 +50,9 @@ def test_reference_test_recipe():
 
 @pytest.mark.parametrize("dtype,wdtype", [(torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32),
                                           (torch.float16, torch.float16), (torch.float32, torch.float32)])
-@pytest.mark.parametrize("rows,dim", [(1, 8), (37, 255), (300, 1024), (64, 4096), (700, 4104), (5, 16384), (9, 5000)])
+@pytest.mark.parametrize("rows,dim", [(1, 8), (37, 255), (300, 1024), (64, 4096), (700, 4104), (5, 16384), (9, 5000),
+                                      # 1024 rows and more of 2 .. 16 KB: the streaming kernels (bulk-copy ring)
+                                      (1024, 1024), (3000, 4096), (1100, 4104), (2500, 2048), (1029, 8192)])
 def test_forward_backward_against_fp64_math(dtype, wdtype, rows, dim):
     from tritonops_b200 import ops
     g = torch.Generator().manual_seed(rows * 31 + dim)
@@ -69,6 +71,26 @@ def test_forward_backward_against_fp64_math(dtype, wdtype, rows, dim):
     # deterministic (fixed summation order for dweight)
     dx2, dw2 = ops.rmsnorm_bwd(dy.cuda(), x.cuda(), w.cuda(), rstd)
     assert torch.equal(dw, dw2) and torch.equal(dx, dx2)
+
+
+def test_streaming_kernels_repeat_and_take_strided_rows():
+    """Many back-to-back calls of the streaming kernels on a shape that keeps every SM's ring full
+    (bulk copies landing out of order must not confuse the slot barriers), with rows that are a
+    strided view; every call must give the first call's bits."""
+    from tritonops_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    big = torch.randn(20000, 2 * 4096, generator=g).to(torch.bfloat16).cuda()
+    x, dy = big[:, :4096], big[:, 4096:]                  # row stride 8192 elements
+    w = (1 + 0.1 * torch.randn(4096, generator=g)).to(torch.bfloat16).cuda()
+    y0, r0 = ops.rmsnorm_fwd(x, w, 1e-6)
+    dx0, dw0 = ops.rmsnorm_bwd(dy, x, w, r0)
+    ry, rr, rdx, rdw = orc.rmsnorm_exact(x[:64].cpu(), w.cpu(), 1e-6, dy[:64].cpu())
+    assert (y0[:64].cpu().double() - ry).abs().max().item() <= 8e-3 * ry.abs().max().item()
+    assert (dx0[:64].cpu().double() - rdx).abs().max().item() <= 8e-3 * max(1.0, rdx.abs().max().item())
+    outs = [(ops.rmsnorm_fwd(x, w, 1e-6), ops.rmsnorm_bwd(dy, x, w, r0)) for _ in range(40)]
+    torch.cuda.synchronize()
+    for (y, r), (dx, dw) in outs:
+        assert torch.equal(y, y0) and torch.equal(r, r0) and torch.equal(dx, dx0) and torch.equal(dw, dw0)
 
 
 def test_strided_rows_empty_and_errors():

@@ -6,14 +6,22 @@
 //   dx_td = r_t (w_d dy_td - x_td r_t^2 mean_d'(dy_td' w_d' x_td'))
 //   dw_d  = sum_t dy_td x_td r_t
 //
-// Forward: one warp per row, two passes over the row (the second one hits L1), 16-byte
-// loads when the row is aligned for them.  Backward: a fixed number of CTAs each walk
-// rows c, c + G, ...; the per-column dw sums stay in registers for the whole walk and
-// are written as one partial row per CTA, which a second kernel adds up in a fixed
-// order (the reference uses fp32 atomics, :217; this is deterministic).  All arithmetic
-// is fp32 whatever the storage type.
+// Large inputs (1024 rows or more of 2 .. 16 KB) take the streaming kernels: persistent CTAs
+// whose producer warp feeds a shared-memory ring with bulk copies.  Otherwise -- forward: one
+// warp per row, two passes over the row (the second one hits L1), 16-byte loads when the row
+// is aligned for them; backward: a fixed number of CTAs each walk rows c, c + G, ....  In every
+// backward form the per-column dw sums stay in registers for the whole walk and leave as one
+// partial row per CTA, which a second kernel adds up in a fixed order (the reference uses fp32
+// atomics, :217; this is deterministic).  All arithmetic is fp32 whatever the storage type.
 #include "common.cuh"
 #include "sm100.cuh"
+
+// Rows are read once: their bulk copies carry an L2 evict-first hint, which leaves L2 to the
+// output lines that are still collecting writes (forward, bf16 65536 x 4096: 5.50 -> 5.66 TB/s;
+// the same hint on the output stores changed nothing).
+#ifndef B200ATTN_RMS_LOAD_HINT
+#define B200ATTN_RMS_LOAD_HINT 1
+#endif
 
 namespace b200attn {
 namespace {
@@ -132,273 +140,318 @@ rmsnorm_fwd_reg_kernel(const XT* __restrict__ x, const WT* __restrict__ w, XT* _
 }
 
 // ---------------------------------------------------------------------------
-// Streaming forward for rows of 2 .. 16 KB: one persistent CTA per SM; a producer warp brings
-// groups of rows into a three-stage ring of 64 KB stages with untiled bulk copies, so the bytes
-// in flight per SM are set by the ring (up to 192 KB) instead of by how many loads the resident
-// warps have outstanding, and eight consumer warps take one row each: sum of squares from
-// shared memory, then scale and store with 16-byte stores.  The weights sit in shared memory as
-// fp32 for the whole kernel.
+// Streaming kernels for rows of 2 .. 16 KB: one persistent CTA per SM.  A producer warp brings
+// the CTA's rows (blockIdx.x, blockIdx.x + gridDim.x, ...) one per slot into a 192 KB ring with
+// untiled bulk copies, so the bytes in flight per SM are set by the ring instead of by how many
+// loads the resident warps have outstanding; consumer warps take the rows in turn from shared
+// memory.  The weights sit in shared memory as fp32 for the whole kernel.  The consumers'
+// instruction streams are chains of dependent operations, so the kernels need many of them:
+// with 8 consumer warps both were bound by issue latency (1.4 .. 1.8 instructions per clock
+// per SM at 2 warps per scheduler), hence 16 / 14.
+// Row `it` of the CTA lives in slot it % n_slots, whoever consumes it.  A slot's barriers are
+// therefore read by different consumers in turn, and a phase parity alone cannot tell "my row
+// has landed" from "the row before the previous one had landed" (bulk copies may complete out
+// of order, so the row in between, another consumer's, may still be in flight).  Hence a
+// consumer first waits until the slot's previous row has been released (the same wait the
+// producer does before refilling it) and only then for its own row: from that point the only
+// phase the slot's full barrier can complete is this row's.
 // ---------------------------------------------------------------------------
-constexpr int kStreamConsumers = 8;
-constexpr int kStreamThreads = 32 * (kStreamConsumers + 1);
-constexpr int kStreamStages = 3;
-constexpr int kStreamStageBytes = 64 * 1024;
+constexpr int kRingBytes = 192 * 1024;
+constexpr int kMaxSlots = 96;
 
 struct StreamSmem {
-  static constexpr int kWeights = kStreamStages * kStreamStageBytes;       // fp32 [D]
-  static int bars(int D) { return kWeights + ((D * 4 + 127) & ~127); }
-  static int bytes(int D) { return bars(D) + 2 * kStreamStages * 8 + 16 + 128; }   // + slack to align the base
+  static constexpr int kWeights = kRingBytes;                                  // fp32 [D]
+  __host__ __device__ static int bars(int D) { return kWeights + ((D * 4 + 127) & ~127); }
+  static int bytes(int D) { return bars(D) + 2 * kMaxSlots * 8 + 16 + 128; }   // + slack to align the base
 };
 
+// ---- forward: a row per consumer warp: sum of squares, then y = x r w written over the row in
+// its slot and sent out as one bulk store.
+constexpr int kFwdStreamConsumers = 16;
+constexpr int kFwdStreamThreads = 32 * (kFwdStreamConsumers + 1);
+
 template <typename XT, typename WT>
-__global__ void __launch_bounds__(kStreamThreads, 1)
+__global__ void __launch_bounds__(kFwdStreamThreads, 1)
 rmsnorm_fwd_stream_kernel(const XT* __restrict__ x, const WT* __restrict__ w, XT* __restrict__ y,
                           float* __restrict__ rstd, long long rows, int D, long long xs, long long ys, float eps,
-                          int rows_per_stage, int* status_word) {
+                          int slot_bytes, int n_slots) {
   using namespace sm100;
   constexpr int N = Vec16<XT>::N;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 127u) & ~127u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   float* sw = reinterpret_cast<float*>(sgen + StreamSmem::kWeights);
-  const int bar_off = StreamSmem::kWeights + ((D * 4 + 127) & ~127);
+  const int bar_off = StreamSmem::bars(D);
   const uint32_t bars = sbase + bar_off;
   auto full = [&](int s) { return bars + 8 * s; };
-  auto empty = [&](int s) { return bars + 8 * (kStreamStages + s); };
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + bar_off + 2 * kStreamStages * 8);
+  auto empty = [&](int s) { return bars + 8 * (kMaxSlots + s); };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + bar_off + 2 * kMaxSlots * 8);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t row_bytes = (uint32_t)D * sizeof(XT);
-  const long long n_groups = (rows + rows_per_stage - 1) / rows_per_stage;
+  const long long my_rows = rows > blockIdx.x ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < kStreamStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), kStreamConsumers); }
+    for (int s = 0; s < n_slots; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
     fence_barrier_init();
     fence_proxy_async();
   }
   __syncthreads();
+  auto slot_of = [&](long long it) { return (int)(it % n_slots); };
+  auto use_of = [&](long long it) { return (uint32_t)((it / n_slots) & 1); };      // phase parity of row `it` in its slot
 
-  if (warp == kStreamConsumers) {
+  if (warp == kFwdStreamConsumers) {
     // ================================================================ producer
     if (lane == 0) {
-      int it = 0, issued = 0;
-      for (long long g = blockIdx.x; g < n_groups; g += gridDim.x, ++it, ++issued) {
-        const int s = it % kStreamStages;
-        if (!mbar_wait(empty(s), ((it / kStreamStages) & 1) ^ 1, abort_flag)) break;
-        const long long r0 = g * rows_per_stage;
-        const int n = (int)min((long long)rows_per_stage, rows - r0);
-        mbar_expect_tx(full(s), (uint32_t)n * row_bytes);
-        for (int r = 0; r < n; ++r)
-          bulk_load_1d(sbase + s * kStreamStageBytes + r * row_bytes, x + (r0 + r) * xs, row_bytes, full(s));
+      long long issued = 0;
+#if B200ATTN_RMS_LOAD_HINT
+      const uint64_t pol = l2_policy_evict_first();
+#endif
+      for (long long it = 0; it < my_rows; ++it, ++issued) {
+        const int s = slot_of(it);
+        if (!mbar_wait(empty(s), use_of(it) ^ 1u, abort_flag)) break;
+        mbar_expect_tx(full(s), row_bytes);
+#if B200ATTN_RMS_LOAD_HINT
+        bulk_load_1d_hint(sbase + s * slot_bytes, x + (blockIdx.x + it * gridDim.x) * xs, row_bytes, full(s), pol);
+#else
+        bulk_load_1d(sbase + s * slot_bytes, x + (blockIdx.x + it * gridDim.x) * xs, row_bytes, full(s));
+#endif
       }
-      if (*abort_flag)      // the consumers no longer wait for the stages: no copy may outlive the CTA
-        for (int i = max(issued - kStreamStages, 0); i < issued; ++i)
-          mbar_drain(full(i % kStreamStages), (i / kStreamStages) & 1);
+      if (*abort_flag) {    // the consumers no longer wait for the slots: no copy may outlive the CTA
+        for (long long i = issued > n_slots ? issued - n_slots : 0; i < issued; ++i) mbar_drain(full(slot_of(i)), use_of(i));
+      }
     }
     return;
   }
 
   // ==================================================================== consumers
-  for (int c = threadIdx.x; c < D; c += 32 * kStreamConsumers) sw[c] = to_f(w[c]);
-  asm volatile("bar.sync 1, %0;" ::"n"(32 * kStreamConsumers) : "memory");
+  for (int c = threadIdx.x; c < D; c += 32 * kFwdStreamConsumers) sw[c] = to_f(w[c]);
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * kFwdStreamConsumers) : "memory");
   const float inv_d = 1.f / (float)D;
   const int chunks = D / N;
-  int it = 0;
-  for (long long g = blockIdx.x; g < n_groups; g += gridDim.x, ++it) {
-    const int s = it % kStreamStages;
-    if (!mbar_wait(full(s), (it / kStreamStages) & 1, abort_flag)) break;
-    const long long r0 = g * rows_per_stage;
-    const int n = (int)min((long long)rows_per_stage, rows - r0);
-    for (int r = warp; r < n; r += kStreamConsumers) {
-      const uint8_t* srow = sgen + s * kStreamStageBytes + (size_t)r * row_bytes;
-      float ss0 = 0.f, ss1 = 0.f;
+  for (long long it = warp; it < my_rows; it += kFwdStreamConsumers) {
+    const int s = slot_of(it);
+    if (!mbar_wait(empty(s), use_of(it) ^ 1u, abort_flag)) break;     // the slot's previous row has been released ...
+    if (!mbar_wait(full(s), use_of(it), abort_flag)) break;           // ... so this can only be row `it` landing
+    const long long row = blockIdx.x + it * gridDim.x;
+    uint8_t* srow = sgen + (size_t)s * slot_bytes;
+    float ss0 = 0.f, ss1 = 0.f;
 #pragma unroll 4
-      for (int c = lane; c < chunks; c += 32) {
-        const Vec16<XT> v = *reinterpret_cast<const Vec16<XT>*>(srow + 16 * c);
+    for (int c = lane; c < chunks; c += 32) {
+      const Vec16<XT> v = *reinterpret_cast<const Vec16<XT>*>(srow + 16 * c);
 #pragma unroll
-        for (int i = 0; i < N; i += 2) {
-          const float f0 = to_f(v.v[i]), f1 = to_f(v.v[i + 1]);
-          ss0 = fmaf(f0, f0, ss0);
-          ss1 = fmaf(f1, f1, ss1);
-        }
+      for (int i = 0; i < N; i += 2) {
+        const float f0 = to_f(v.v[i]), f1 = to_f(v.v[i + 1]);
+        ss0 = fmaf(f0, f0, ss0);
+        ss1 = fmaf(f1, f1, ss1);
       }
-      float ss = ss0 + ss1;
+    }
+    float ss = ss0 + ss1;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const float rr = 1.f / sqrtf(eps + ss * inv_d);   // the reference's form (common/rms.py:68)
-      XT* yr = y + (r0 + r) * ys;
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rr = 1.f / sqrtf(eps + ss * inv_d);   // the reference's form (common/rms.py:68)
 #pragma unroll 4
-      for (int c = lane; c < chunks; c += 32) {
-        const Vec16<XT> v = *reinterpret_cast<const Vec16<XT>*>(srow + 16 * c);
-        Vec16<XT> o;
+    for (int c = lane; c < chunks; c += 32) {
+      const Vec16<XT> v = *reinterpret_cast<const Vec16<XT>*>(srow + 16 * c);
+      Vec16<XT> o;
 #pragma unroll
-        for (int i = 0; i < N; i += 4) {
-          const float4 wf = *reinterpret_cast<const float4*>(sw + c * N + i);
-          o.v[i] = from_f<XT>(to_f(v.v[i]) * rr * wf.x);
-          o.v[i + 1] = from_f<XT>(to_f(v.v[i + 1]) * rr * wf.y);
-          o.v[i + 2] = from_f<XT>(to_f(v.v[i + 2]) * rr * wf.z);
-          o.v[i + 3] = from_f<XT>(to_f(v.v[i + 3]) * rr * wf.w);
-        }
-        *reinterpret_cast<Vec16<XT>*>(yr + c * N) = o;
+      for (int i = 0; i < N; i += 4) {
+        const float4 wf = *reinterpret_cast<const float4*>(sw + c * N + i);
+        o.v[i] = from_f<XT>(to_f(v.v[i]) * rr * wf.x);
+        o.v[i + 1] = from_f<XT>(to_f(v.v[i + 1]) * rr * wf.y);
+        o.v[i + 2] = from_f<XT>(to_f(v.v[i + 2]) * rr * wf.z);
+        o.v[i + 3] = from_f<XT>(to_f(v.v[i + 3]) * rr * wf.w);
       }
-      if (lane == 0 && rstd) rstd[r0 + r] = rr;
+      *reinterpret_cast<Vec16<XT>*>(srow + 16 * c) = o;     // each lane rewrites the chunks it read
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+      bulk_store_1d(y + row * ys, sbase + s * slot_bytes, row_bytes);
+      bulk_commit_group();
+      if (rstd) rstd[row] = rr;
+      bulk_wait_read_all();          // the slot may be refilled once the store has read it
+      mbar_arrive(empty(s));
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(empty(s));
   }
-  if (threadIdx.x == 0 && *abort_flag && status_word) atomicExch(status_word, 1);
+  if (lane == 0) bulk_wait_all();     // no store of this thread may outlive the CTA
 }
 
-// ---------------------------------------------------------------------------
-// Streaming backward, rows of at least 2 KB and at most 4096 columns: one persistent CTA per SM.
-// The ring holds (x row, dy row) pairs in slots of 16 KB filled by the producer warp in row
-// order; consumer warp i takes the CTA's rows i, i + 8, ...: pass 1 sums dy w x over the row,
-// pass 2 writes dx and adds dy x r into per-column dw sums that stay in the lane's registers
-// for the whole kernel (CH 16-byte chunks per lane).  At the end the eight warps' dw rows are
-// added in a fixed order through the (by then idle) ring and leave as one partial row per CTA.
-// ---------------------------------------------------------------------------
-constexpr int kBwdSlotBytes = 16 * 1024;
-// seven consumer warps and the producer: 256 threads, so a consumer lane may hold the 128 dw sums
-// of its columns and its working set in registers (nine warps would cap it at 168)
-constexpr int kBwdStreamConsumers = 7;
+// ---- backward, at most 4096 columns: a row (x and dy) per PAIR of consumer warps, each warp
+// half of the row's 16-byte chunks.  Pass 1 sums dy w x over the row (the two halves meet in
+// shared memory, added in a fixed order), pass 2 writes dx over x in the slot (one bulk store
+// per row) and adds dy x r into per-column dw sums that stay in the lane's registers for the
+// whole kernel (CH chunks per lane).  At the end the pairs' dw rows are added in pair order
+// through the (by then idle) ring and leave as one partial row per CTA.
+constexpr int kBwdPairs = 7;
+constexpr int kBwdStreamConsumers = 2 * kBwdPairs;
 constexpr int kBwdStreamThreads = 32 * (kBwdStreamConsumers + 1);
-constexpr int kBwdSlots = kStreamStages * kStreamStageBytes / kBwdSlotBytes;   // 12
-
-struct StreamBwdSmem {
-  static constexpr int kWeights = kBwdSlots * kBwdSlotBytes;
-  static int bars(int D) { return kWeights + ((D * 4 + 127) & ~127); }
-  static int bytes(int D) { return bars(D) + 2 * kBwdSlots * 8 + 16 + 128; }
-};
 
 template <typename XT, typename WT, int CH>
 __global__ void __launch_bounds__(kBwdStreamThreads, 1)
 rmsnorm_bwd_stream_kernel(const XT* __restrict__ dy, const XT* __restrict__ x, const WT* __restrict__ w,
                           const float* __restrict__ rstd, XT* __restrict__ dx, float* __restrict__ partial,
-                          long long rows, int D, long long dys, long long xs, long long dxs) {
+                          long long rows, int D, long long dys, long long xs, long long dxs, int slot_bytes,
+                          int n_slots) {
   using namespace sm100;
   constexpr int N = Vec16<XT>::N;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 127u) & ~127u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
-  float* sw = reinterpret_cast<float*>(sgen + StreamBwdSmem::kWeights);
-  const int bar_off = StreamBwdSmem::kWeights + ((D * 4 + 127) & ~127);
+  float* sw = reinterpret_cast<float*>(sgen + StreamSmem::kWeights);
+  const int bar_off = StreamSmem::bars(D);
   const uint32_t bars = sbase + bar_off;
   auto full = [&](int s) { return bars + 8 * s; };
-  auto empty = [&](int s) { return bars + 8 * (kBwdSlots + s); };
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + bar_off + 2 * kBwdSlots * 8);
+  auto empty = [&](int s) { return bars + 8 * (kMaxSlots + s); };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + bar_off + 2 * kMaxSlots * 8);
+  __shared__ float pair_sum[kBwdPairs][2][2];     // [pair][row parity][half]
+  __shared__ int pair_ok[kBwdPairs][2][2];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t row_bytes = (uint32_t)D * sizeof(XT);
-  // this CTA's rows: blockIdx.x, blockIdx.x + gridDim.x, ...
   const long long my_rows = rows > blockIdx.x ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < kBwdSlots; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+    for (int s = 0; s < n_slots; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 2); }
     fence_barrier_init();
     fence_proxy_async();
   }
   __syncthreads();
+  auto slot_of = [&](long long it) { return (int)(it % n_slots); };
+  auto use_of = [&](long long it) { return (uint32_t)((it / n_slots) & 1); };      // phase parity of row `it` in its slot
 
   if (warp == kBwdStreamConsumers) {
     // ================================================================ producer
     if (lane == 0) {
       long long issued = 0;
+#if B200ATTN_RMS_LOAD_HINT
+      const uint64_t pol = l2_policy_evict_first();
+#endif
       for (long long it = 0; it < my_rows; ++it, ++issued) {
-        const int s = (int)(it % kBwdSlots);
-        if (!mbar_wait(empty(s), (uint32_t)((it / kBwdSlots) & 1) ^ 1u, abort_flag)) break;
+        const int s = slot_of(it);
+        if (!mbar_wait(empty(s), use_of(it) ^ 1u, abort_flag)) break;
         const long long row = blockIdx.x + it * gridDim.x;
         mbar_expect_tx(full(s), 2 * row_bytes);
-        bulk_load_1d(sbase + s * kBwdSlotBytes, x + row * xs, row_bytes, full(s));
-        bulk_load_1d(sbase + s * kBwdSlotBytes + kBwdSlotBytes / 2, dy + row * dys, row_bytes, full(s));
+#if B200ATTN_RMS_LOAD_HINT
+        bulk_load_1d_hint(sbase + s * slot_bytes, x + row * xs, row_bytes, full(s), pol);
+        bulk_load_1d_hint(sbase + s * slot_bytes + slot_bytes / 2, dy + row * dys, row_bytes, full(s), pol);
+#else
+        bulk_load_1d(sbase + s * slot_bytes, x + row * xs, row_bytes, full(s));
+        bulk_load_1d(sbase + s * slot_bytes + slot_bytes / 2, dy + row * dys, row_bytes, full(s));
+#endif
       }
-      if (*abort_flag)
-        for (long long i = issued > kBwdSlots ? issued - kBwdSlots : 0; i < issued; ++i)
-          mbar_drain(full((int)(i % kBwdSlots)), (uint32_t)((i / kBwdSlots) & 1));
+      if (*abort_flag) {
+        for (long long i = issued > n_slots ? issued - n_slots : 0; i < issued; ++i) mbar_drain(full(slot_of(i)), use_of(i));
+      }
     }
-  } else {
-    // ================================================================== consumers
-    for (int c = threadIdx.x; c < D; c += 32 * kBwdStreamConsumers) sw[c] = to_f(w[c]);
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * kBwdStreamConsumers) : "memory");
-    const float inv_d = 1.f / (float)D;
-    const int chunks = D / N;
-    float dwv[CH][N];
+    return;
+  }
+
+  // ==================================================================== consumers
+  for (int c = threadIdx.x; c < D; c += 32 * kBwdStreamConsumers) sw[c] = to_f(w[c]);
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * kBwdStreamConsumers) : "memory");
+  const int pair = warp >> 1, half = warp & 1;
+  const float inv_d = 1.f / (float)D;
+  const int chunks = D / N;
+  // this lane's chunks: (2 k + half) * 32 + lane, k < CH
+  float dwv[CH][N];
 #pragma unroll
-    for (int k = 0; k < CH; ++k)
+  for (int k = 0; k < CH; ++k)
 #pragma unroll
-      for (int i = 0; i < N; ++i) dwv[k][i] = 0.f;
-    for (long long it = warp; it < my_rows; it += kBwdStreamConsumers) {
-      const int s = (int)(it % kBwdSlots);
-      if (!mbar_wait(full(s), (uint32_t)((it / kBwdSlots) & 1), abort_flag)) break;
-      const long long row = blockIdx.x + it * gridDim.x;
-      const uint8_t* sx = sgen + s * kBwdSlotBytes;
-      const uint8_t* sg = sx + kBwdSlotBytes / 2;
-      const float r = rstd[row];
-      float t0 = 0.f, t1 = 0.f;
+    for (int i = 0; i < N; ++i) dwv[k][i] = 0.f;
+  long long n_done = 0;
+  for (long long it = pair; it < my_rows; it += kBwdPairs, ++n_done) {
+    const int s = slot_of(it);
+    // (a wait that gave up is carried to the pair's barrier below, so that both warps of the
+    // pair leave the loop together and neither waits for the other for ever)
+    // first "the slot's previous row has been released", then "this row has landed" (see above)
+    const bool landed = mbar_wait(empty(s), use_of(it) ^ 1u, abort_flag) && mbar_wait(full(s), use_of(it), abort_flag);
+    const long long row = blockIdx.x + it * gridDim.x;
+    uint8_t* sx = sgen + (size_t)s * slot_bytes;
+    const uint8_t* sg = sx + slot_bytes / 2;
+    const float r = rstd[row];
+    float t0 = 0.f, t1 = 0.f;
 #pragma unroll
-      for (int k = 0; k < CH; ++k) {
-        const int c = lane + 32 * k;
-        if (c < chunks) {
-          const Vec16<XT> xv = *reinterpret_cast<const Vec16<XT>*>(sx + 16 * c);
-          const Vec16<XT> gv = *reinterpret_cast<const Vec16<XT>*>(sg + 16 * c);
+    for (int k = 0; k < CH; ++k) {
+      const int c = (2 * k + half) * 32 + lane;
+      if (landed && c < chunks) {
+        const Vec16<XT> xv = *reinterpret_cast<const Vec16<XT>*>(sx + 16 * c);
+        const Vec16<XT> gv = *reinterpret_cast<const Vec16<XT>*>(sg + 16 * c);
 #pragma unroll
-          for (int i = 0; i < N; i += 4) {
-            const float4 wf = *reinterpret_cast<const float4*>(sw + c * N + i);
-            t0 = fmaf(to_f(gv.v[i]) * wf.x, to_f(xv.v[i]), t0);
-            t1 = fmaf(to_f(gv.v[i + 1]) * wf.y, to_f(xv.v[i + 1]), t1);
-            t0 = fmaf(to_f(gv.v[i + 2]) * wf.z, to_f(xv.v[i + 2]), t0);
-            t1 = fmaf(to_f(gv.v[i + 3]) * wf.w, to_f(xv.v[i + 3]), t1);
+        for (int i = 0; i < N; i += 4) {
+          const float4 wf = *reinterpret_cast<const float4*>(sw + c * N + i);
+          t0 = fmaf(to_f(gv.v[i]) * wf.x, to_f(xv.v[i]), t0);
+          t1 = fmaf(to_f(gv.v[i + 1]) * wf.y, to_f(xv.v[i + 1]), t1);
+          t0 = fmaf(to_f(gv.v[i + 2]) * wf.z, to_f(xv.v[i + 2]), t0);
+          t1 = fmaf(to_f(gv.v[i + 3]) * wf.w, to_f(xv.v[i + 3]), t1);
+        }
+      }
+    }
+    float tot = t0 + t1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    // meet the other half of the row (a slot of pair_sum per row parity: the barrier keeps the
+    // two warps of a pair within one row of each other)
+    const int par = (int)(n_done & 1);
+    if (lane == 0) { pair_sum[pair][par][half] = tot; pair_ok[pair][par][half] = landed ? 1 : 0; }
+    asm volatile("bar.sync %0, 64;" ::"r"(2 + pair) : "memory");
+    if (!(pair_ok[pair][par][0] && pair_ok[pair][par][1])) break;
+    tot = pair_sum[pair][par][0] + pair_sum[pair][par][1];
+    const float coef = tot * r * r * inv_d;
+#pragma unroll
+    for (int k = 0; k < CH; ++k) {
+      const int c = (2 * k + half) * 32 + lane;
+      if (c < chunks) {
+        const Vec16<XT> xv = *reinterpret_cast<const Vec16<XT>*>(sx + 16 * c);
+        const Vec16<XT> gv = *reinterpret_cast<const Vec16<XT>*>(sg + 16 * c);
+        Vec16<XT> o;
+#pragma unroll
+        for (int i = 0; i < N; i += 4) {
+          const float4 wf = *reinterpret_cast<const float4*>(sw + c * N + i);
+          const float wv[4] = {wf.x, wf.y, wf.z, wf.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float xf = to_f(xv.v[i + j]), gf = to_f(gv.v[i + j]);
+            o.v[i + j] = from_f<XT>(r * (wv[j] * gf - xf * coef));
+            dwv[k][i + j] = fmaf(gf * xf, r, dwv[k][i + j]);
           }
         }
+        *reinterpret_cast<Vec16<XT>*>(sx + 16 * c) = o;      // dx over x: each lane rewrites the chunks it read
       }
-      float tot = t0 + t1;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
-      const float coef = tot * r * r * inv_d;
-      XT* dr = dx + row * dxs;
-#pragma unroll
-      for (int k = 0; k < CH; ++k) {
-        const int c = lane + 32 * k;
-        if (c < chunks) {
-          const Vec16<XT> xv = *reinterpret_cast<const Vec16<XT>*>(sx + 16 * c);
-          const Vec16<XT> gv = *reinterpret_cast<const Vec16<XT>*>(sg + 16 * c);
-          Vec16<XT> o;
-#pragma unroll
-          for (int i = 0; i < N; i += 4) {
-            const float4 wf = *reinterpret_cast<const float4*>(sw + c * N + i);
-            const float wv[4] = {wf.x, wf.y, wf.z, wf.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float xf = to_f(xv.v[i + j]), gf = to_f(gv.v[i + j]);
-              o.v[i + j] = from_f<XT>(r * (wv[j] * gf - xf * coef));
-              dwv[k][i + j] = fmaf(gf * xf, r, dwv[k][i + j]);
-            }
-          }
-          *reinterpret_cast<Vec16<XT>*>(dr + c * N) = o;
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty(s));
     }
-    // ---- the seven dw rows -> one partial row per CTA, added in warp order.  Every slot has
-    // been consumed (or the CTA is aborting and the producer drains): the ring is free.
+    fence_proxy_async();
+    asm volatile("bar.sync %0, 64;" ::"r"(2 + pair) : "memory");   // both halves of dx are in the slot
+    if (lane == 0) {
+      if (half == 0) {
+        bulk_store_1d(dx + row * dxs, sbase + s * slot_bytes, row_bytes);
+        bulk_commit_group();
+        bulk_wait_read_all();        // the slot may be refilled once the store has read it
+      }
+      mbar_arrive(empty(s));
+    }
+    __syncwarp();
+  }
+  if (lane == 0) bulk_wait_all();     // no store of this thread may outlive the CTA
+  // ---- the pairs' dw rows -> one partial row per CTA, added in pair order.  Every slot has been
+  // consumed (or the CTA is aborting and the producer drains): the ring is free.
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * kBwdStreamConsumers) : "memory");
+  if (!*abort_flag) {
+    float* red = reinterpret_cast<float*>(sgen);     // [kBwdPairs][D] fp32 <= 112 KB of the ring
+#pragma unroll
+    for (int k = 0; k < CH; ++k) {
+      const int c = (2 * k + half) * 32 + lane;
+      if (c < chunks) {
+#pragma unroll
+        for (int i = 0; i < N; i += 4)
+          *reinterpret_cast<float4*>(red + (size_t)pair * D + c * N + i) =
+              make_float4(dwv[k][i], dwv[k][i + 1], dwv[k][i + 2], dwv[k][i + 3]);
+      }
+    }
     asm volatile("bar.sync 1, %0;" ::"n"(32 * kBwdStreamConsumers) : "memory");
-    if (!*abort_flag) {
-      float* red = reinterpret_cast<float*>(sgen);     // [7][D] fp32 <= 112 KB of the 192 KB ring
+    for (int c = threadIdx.x; c < D; c += 32 * kBwdStreamConsumers) {
+      float sum = 0.f;
 #pragma unroll
-      for (int k = 0; k < CH; ++k) {
-        const int c = lane + 32 * k;
-        if (c < chunks) {
-#pragma unroll
-          for (int i = 0; i < N; i += 4)
-            *reinterpret_cast<float4*>(red + (size_t)warp * D + c * N + i) =
-                make_float4(dwv[k][i], dwv[k][i + 1], dwv[k][i + 2], dwv[k][i + 3]);
-        }
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(32 * kBwdStreamConsumers) : "memory");
-      for (int c = threadIdx.x; c < D; c += 32 * kBwdStreamConsumers) {
-        float sum = 0.f;
-#pragma unroll
-        for (int wq = 0; wq < kBwdStreamConsumers; ++wq) sum += red[(size_t)wq * D + c];
-        partial[(long long)blockIdx.x * D + c] = sum;
-      }
+      for (int p = 0; p < kBwdPairs; ++p) sum += red[(size_t)p * D + c];
+      partial[(long long)blockIdx.x * D + c] = sum;
     }
   }
 }
@@ -565,16 +618,16 @@ int launch_fwd(const b200attn_rmsnorm_fwd_args* a, cudaStream_t stream) {
   if (vec && row_bytes >= 2048 && row_bytes <= 16384 && a->dim * 4 <= 32768 && a->rows >= 1024) {
     const DeviceInfo* di = nullptr;
     if (int st = device_info(&di)) return st;
-    int per_stage = (int)(kStreamStageBytes / row_bytes);
-    if (per_stage > kStreamConsumers) per_stage = kStreamConsumers;
-    const long long groups = (a->rows + per_stage - 1) / per_stage;
-    const int grid = (int)(groups < di->sm_count ? groups : di->sm_count);
+    const int slot = (int)((row_bytes + 127) & ~127LL);
+    int n_slots = kRingBytes / slot;
+    if (n_slots > kMaxSlots) n_slots = kMaxSlots;
+    const int grid = (int)(a->rows < di->sm_count ? a->rows : di->sm_count);
     auto kern = rmsnorm_fwd_stream_kernel<XT, WT>;
     const int smem = StreamSmem::bytes(a->dim);
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return B200ATTN_ERR_CUDA;
-    kern<<<grid, kStreamThreads, smem, stream>>>((const XT*)a->x, (const WT*)a->weight, (XT*)a->y, a->rstd, a->rows,
-                                               a->dim, a->x_stride_row, a->y_stride_row, a->eps, per_stage, nullptr);
+    kern<<<grid, kFwdStreamThreads, smem, stream>>>((const XT*)a->x, (const WT*)a->weight, (XT*)a->y, a->rstd, a->rows,
+                                                  a->dim, a->x_stride_row, a->y_stride_row, a->eps, slot, n_slots);
     set_launch_count(1);
     return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
   }
@@ -607,25 +660,28 @@ int launch_bwd_rms(const b200attn_rmsnorm_bwd_args* a, cudaStream_t stream) {
                    a->dx_stride_row % N == 0 && (((uintptr_t)a->x | (uintptr_t)a->dy | (uintptr_t)a->dx) & 15) == 0;
   // rows of at least 2 KB, at most 4096 columns (the dw sums of a row live in one warp's registers)
   const long long row_bytes = (long long)a->dim * (long long)sizeof(XT);
-  if (vec && ((uintptr_t)a->weight & 15) == 0 && row_bytes >= 2048 && row_bytes <= kBwdSlotBytes / 2 && a->dim <= 4096 &&
+  if (vec && ((uintptr_t)a->weight & 15) == 0 && row_bytes >= 2048 && row_bytes <= 16384 && a->dim <= 4096 &&
       a->rows >= 1024) {
     const DeviceInfo* di = nullptr;
     if (int st = device_info(&di)) return st;
     const int grid = di->sm_count < g ? di->sm_count : g;     // partial rows: the workspace holds g of them
-    const int smem = StreamBwdSmem::bytes(a->dim);
-    const int ch = (a->dim / N + 31) / 32;                    // 16-byte chunks per lane
+    const int smem = StreamSmem::bytes(a->dim);
+    const int slot = 2 * (int)((row_bytes + 127) & ~127LL);   // x row, dy row
+    int n_slots = kRingBytes / slot;
+    if (n_slots > kMaxSlots) n_slots = kMaxSlots;
+    const int ch = (a->dim / N + 63) / 64;                    // 16-byte chunks per lane (two warps share a row)
 #define B200ATTN_RMS_BWD_STREAM(CH)                                                                               \
   {                                                                                                               \
     auto kern = rmsnorm_bwd_stream_kernel<XT, WT, CH>;                                                            \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)             \
       return B200ATTN_ERR_CUDA;                                                                                   \
     kern<<<grid, kBwdStreamThreads, smem, stream>>>(dy, x, w, a->rstd, dx, partial, a->rows, a->dim, a->dy_stride_row, \
-                                                 a->x_stride_row, a->dx_stride_row);                              \
+                                                 a->x_stride_row, a->dx_stride_row, slot, n_slots);               \
   }
-    if (ch <= 4) B200ATTN_RMS_BWD_STREAM(4)
+    if (ch <= 2) B200ATTN_RMS_BWD_STREAM(2)
+    else if (ch <= 4) B200ATTN_RMS_BWD_STREAM(4)
     else if (ch <= 8) B200ATTN_RMS_BWD_STREAM(8)
-    else if (ch <= 16) B200ATTN_RMS_BWD_STREAM(16)
-    else if constexpr (N == 4) B200ATTN_RMS_BWD_STREAM(32)     // (fp32 rows: 4 columns per chunk)
+    else if constexpr (N == 4) B200ATTN_RMS_BWD_STREAM(16)     // (fp32 rows: 4 columns per chunk)
 #undef B200ATTN_RMS_BWD_STREAM
     rmsnorm_dw_reduce_kernel<WT><<<(a->dim + 255) / 256, 256, 0, stream>>>(partial, (WT*)a->dweight, a->dim, grid);
     set_launch_count(2);
