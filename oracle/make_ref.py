@@ -3,7 +3,7 @@ machine, where the reference checkout itself does not exist.
 
     REFERENCE_ROOT=<checkout of rookie-joe/TritonOps> python -m oracle.make_ref
 
-Copies flash_attn_triton/*.py and utils/utils.py, unmodified, into oracle/_ref/ (git-ignored: the
+Copies flash_attn_triton/*.py, utils/utils.py and common/rms.py, unmodified, into oracle/_ref/ (git-ignored: the
 reference's sources never enter this repository's history).  The staged modules are test
 infrastructure like the rest of oracle/: the GPU parity tests run the reference's Triton kernels
 from there beside this library's kernels, and bench.py times them as a second baseline.  Nothing
@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(HERE, "_ref")
 FILES = [("flash_attn_triton", "flash_attn_triton.py"), ("flash_attn_triton", "flash_attn_decoding.py"),
          ("flash_attn_triton", "flash_attn_decoding_sparse.py"), ("flash_attn_triton", "flash_attn_sparse_attn_triton.py"),
-         ("utils", "utils.py")]
+         ("utils", "utils.py"), ("common", "rms.py")]
 
 
 def reference_root():

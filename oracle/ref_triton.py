@@ -78,6 +78,28 @@ def window_prefill(q, k, v, cu, local, glob, scale=None):
     return o, lse
 
 
+def dense_prefill_grads(q, k, v, cu, d_o):
+    """Forward and backward through the reference's autograd function (flash_attn_triton.py:816-874):
+    its three backward kernels (:184-592) and the host-side GQA sum (:813).  Returns (o, dq, dk, dv)."""
+    dense = load()[0]
+    q, k, v = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    o = dense.flash_attn_triton.apply(q, k, v, cu)
+    o.backward(d_o)
+    return o.detach(), q.grad, k.grad, v.grad
+
+
+def rmsnorm_module(dim, eps, weight):
+    """The reference's RMSNormTriton module (common/rms.py:358-382) with the given weight."""
+    import torch
+    if REF_DIR not in sys.path:
+        sys.path.insert(0, REF_DIR)
+    rms = importlib.import_module("common.rms")
+    m = rms.RMSNormTriton(dim, eps).to(weight.device)
+    with torch.no_grad():
+        m.weight.copy_(weight)
+    return m
+
+
 def window_kernel_matches_its_oracle(local, glob) -> bool:
     return glob < 128 or local >= 128 * (glob // 128)
 

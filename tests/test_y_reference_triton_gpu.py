@@ -107,3 +107,52 @@ def test_sparse_decoding_vs_reference_kernels(dtype, glob, local):
     ro = reference(ref_triton.sparse_decoding, q, kc, vc, cu, glob, local)
     o = flash_attention_sparse_decoding(q, kc, vc, cu, glob, local)
     assert maxabs(o, ro) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("lens,hq,hkv,d", [
+    ([256, 131], 8, 4, 128),                     # two of the reference test's configs, flash_attn_triton.py:1005-1009
+    ([512, 33, 400, 1], 4, 1, 64)])              # (each head dim makes the reference autotune its kernels again: ~1 min)
+def test_backward_vs_reference_kernels(lens, hq, hkv, d):
+    """dQ, dK, dV of this library against the reference's three backward kernels and host-side
+    GQA sum (flash_attn_triton.py:184-592, :661-813), both under autograd on the GPU, with the
+    reference test's own inputs (bf16 U[0,1)) and tolerances (1e-2 on dq / dk widened to 2e-2 for
+    bf16 operands, 1e-1 on dv; :1086-1089)."""
+    from tritonops_b200.flash_attn_triton.flash_attn_triton import flash_attn_triton
+    q, k, v, cu = packed(lens, hq, hkv, d, torch.bfloat16, seed=d, dist="rand")
+    do = torch.randn(q.shape, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).cuda()
+    ro, rdq, rdk, rdv = reference(ref_triton.dense_prefill_grads, q, k, v, cu, do)
+    qq, kk, vv = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    o = flash_attn_triton.apply(qq, kk, vv, cu)
+    o.backward(do)
+    assert maxabs(o, ro) <= 2e-2
+    for ours, ref, tol in ((qq.grad, rdq, 2e-2), (kk.grad, rdk, 2e-2), (vv.grad, rdv, 1e-1)):
+        bad = (ours.float() - ref.float()).abs() > tol + tol * ref.float().abs()
+        assert not bool(bad.any()), f"max err {maxabs(ours, ref):.4g}, {int(bad.sum())} elements off"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,dim", [(64, 128), (300, 1024), (2048, 4096), (37, 4104)])
+def test_rmsnorm_forward_vs_reference_kernel(dtype, rows, dim):
+    """RMSNorm forward against the reference's Triton kernel (common/rms.py:9-88) through its
+    module; the 2048 x 4096 case takes this library's streaming kernel.  (The reference's Triton
+    backward multiplies dy of one 128-wide block with the weights of another when dim > 128,
+    :197-199, so only dim <= 128 gradients are compared.)"""
+    from tritonops_b200.common.rms import RMSNormTriton
+    g = torch.Generator().manual_seed(rows + dim)
+    x = torch.randn(rows, dim, generator=g).to(dtype).cuda()
+    w = (1 + 0.1 * torch.randn(dim, generator=g)).to(dtype).cuda()
+    dy = torch.randn(rows, dim, generator=g).to(dtype).cuda()
+    ref_mod = reference(ref_triton.rmsnorm_module, dim, 1e-6, w)
+    xr = x.clone().requires_grad_(True)
+    ry = reference(ref_mod.to(dtype), xr)
+    ours = RMSNormTriton(dim, 1e-6).to("cuda").to(dtype)
+    with torch.no_grad():
+        ours.weight.copy_(w)
+    xo = x.clone().requires_grad_(True)
+    y = ours(xo)
+    rel = {torch.float32: 1e-5, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dtype]
+    assert maxabs(y, ry) <= rel * max(1.0, ry.float().abs().max().item())
+    if dim <= 128:
+        reference(lambda: ry.backward(dy))
+        y.backward(dy)
+        assert maxabs(xo.grad, xr.grad) <= rel * max(1.0, xr.grad.float().abs().max().item())
