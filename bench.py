@@ -43,14 +43,14 @@ LOG2E = 1.4426950408889634
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the named kernel and the ncu summary
 # the figure comes from (same workload unless the summary says it was scaled)
 TRAFFIC = {
-    "cfg2": (409.803520e6 + 120.196096e6, "profiles/prefill_cfg2_ncu.md"),
-    "cfg3": (1.301270e9 + 6.896384e6, "profiles/decode_cfg3_ncu.md"),
-    "cfg2_backward": (809.810176e6 + 491.803392e6, "profiles/backward_cfg2_ncu.md"),
-    "cfg4": (619.421184e6 + 128.075264e6, "profiles/sparse_prefill_cfg4_ncu.md"),
-    "cfg5": (2.148035e9 + 14.810368e6, "profiles/sparse_decode_cfg5_ncu.md (batch 8 capture x 4)"),
-    "paged_cfg3": (None, None),
-    "rmsnorm_fwd": (None, None),
-    "rmsnorm_bwd": (None, None),
+    "cfg2": (409.738496e6 + 119.315968e6, "profiles/prefill_cfg2_ncu.md"),
+    "cfg3": (1.301250e9 + 6.312448e6, "profiles/decode_cfg3_ncu.md"),
+    "cfg2_backward": (809.637120e6 + 491.812352e6, "profiles/backward_cfg2_ncu.md"),
+    "cfg4": (614.754816e6 + 124.699136e6, "profiles/sparse_prefill_cfg4_ncu.md"),
+    "cfg5": (4 * (537.079552e6 + 4.031488e6), "profiles/sparse_decode_cfg5_ncu.md (batch 8 capture x 4)"),
+    "paged_cfg3": (1.301388e9 + 6.204160e6, "profiles/paged_decode_cfg3_ncu.md"),
+    "rmsnorm_fwd": (537.041920e6 + 480.131072e6, "profiles/rmsnorm_ncu.md (one cold launch: 57 MB of the output still in L2)"),
+    "rmsnorm_bwd": (1.074061e9 + 480.250624e6, "profiles/rmsnorm_ncu.md (one cold launch)"),
 }
 
 
