@@ -759,6 +759,8 @@ def run_ours(args, rank, world, local_rank, cpu_base):
         if "cfg2_kernel_ms" in ref_gpu:
             ref_gpu["cfg2_speedup_kernel"] = ref_gpu["cfg2_kernel_ms"] / ms
             ref_gpu["cfg2_speedup_wrapper"] = ref_gpu["cfg2_wrapper_ms"] / ms
+        if "cfg2_backward_wrapper_ms" in ref_gpu and "ms_per_step" in rl.get("backward_cfg2", {}):
+            ref_gpu["cfg2_backward_speedup"] = ref_gpu["cfg2_backward_wrapper_ms"] / rl["backward_cfg2"]["ms_per_step"]
         if "cfg3_wrapper_ms" in ref_gpu and "ms_per_step" in rl.get("decode_cfg3", {}):
             ref_gpu["cfg3_speedup_wrapper"] = ref_gpu["cfg3_wrapper_ms"] / rl["decode_cfg3"]["ms_per_step"]
         rl["reference_triton_gpu"] = ref_gpu

@@ -158,6 +158,21 @@ def bench_on_gpu():
         del w, o, lse
     except Exception as e:  # noqa: BLE001
         out["cfg2_error"] = f"{type(e).__name__}: {str(e)[:300]}"
+    if os.environ.get("B200ATTN_BENCH_REF_BACKWARD"):
+        # forward + backward through the reference's autograd function (its backward kernels
+        # autotune for about a minute at this size, so only on request)
+        try:
+            w = workloads.dense_causal(4, 32, 4096, 128, 1, dev, name="cfg2")
+            do = torch.randn(w.q.shape, device=dev, dtype=torch.float32).to(w.q.dtype)
+            dense = load()[0]
+            o, lse = dense.flash_attn_triton_fwd(w.q, w.k, w.v, w.cu_seqlens, 128 ** -0.5 * LOG2E)
+            fb = lambda: dense.flash_attn_triton_bwd(w.q, w.k, w.v, o, do, lse, w.cu_seqlens, 128 ** -0.5 * LOG2E)
+            fb()
+            out["cfg2_backward_wrapper_ms"] = _events_ms(fb, 5, 2)
+            out["cfg2_backward_tflops"] = 2.5 * w.flops / out["cfg2_backward_wrapper_ms"] / 1e9
+            del w, do, o, lse
+        except Exception as e:  # noqa: BLE001
+            out["cfg2_backward_error"] = f"{type(e).__name__}: {str(e)[:300]}"
     try:
         w3 = workloads.cfg3(dev)
         decoding(w3.q, w3.k_cache, w3.v_cache, w3.cu_seqlens)
