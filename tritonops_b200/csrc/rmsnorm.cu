@@ -660,8 +660,9 @@ int launch_bwd_rms(const b200attn_rmsnorm_bwd_args* a, cudaStream_t stream) {
                    a->dx_stride_row % N == 0 && (((uintptr_t)a->x | (uintptr_t)a->dy | (uintptr_t)a->dx) & 15) == 0;
   // rows of at least 2 KB, at most 4096 columns (the dw sums of a row live in one warp's registers)
   const long long row_bytes = (long long)a->dim * (long long)sizeof(XT);
+  const int ch = (a->dim / N + 63) / 64;                      // 16-byte chunks per lane (two warps share a row)
   if (vec && ((uintptr_t)a->weight & 15) == 0 && row_bytes >= 2048 && row_bytes <= 16384 && a->dim <= 4096 &&
-      a->rows >= 1024) {
+      ch <= (N == 4 ? 16 : 8) && a->rows >= 1024) {
     const DeviceInfo* di = nullptr;
     if (int st = device_info(&di)) return st;
     const int grid = di->sm_count < g ? di->sm_count : g;     // partial rows: the workspace holds g of them
@@ -669,7 +670,6 @@ int launch_bwd_rms(const b200attn_rmsnorm_bwd_args* a, cudaStream_t stream) {
     const int slot = 2 * (int)((row_bytes + 127) & ~127LL);   // x row, dy row
     int n_slots = kRingBytes / slot;
     if (n_slots > kMaxSlots) n_slots = kMaxSlots;
-    const int ch = (a->dim / N + 63) / 64;                    // 16-byte chunks per lane (two warps share a row)
 #define B200ATTN_RMS_BWD_STREAM(CH)                                                                               \
   {                                                                                                               \
     auto kern = rmsnorm_bwd_stream_kernel<XT, WT, CH>;                                                            \
