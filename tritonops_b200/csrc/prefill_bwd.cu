@@ -77,7 +77,7 @@ struct BwdSmem {
   static constexpr int kStagePanel = kT * 128;
   static_assert((DP / 64) * kStagePanel <= kPds && (DP / 64) * kStagePanel <= kOperand, "dQ staging fits");
   static constexpr int kBarOffset = kQ1 + kOperand;
-  static constexpr int kNumBars = 9;
+  static constexpr int kNumBars = 10;
   static constexpr int kBytes = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kAlloc = kBytes + 1024;
 };
@@ -114,7 +114,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t bars = sbase + L::kBarOffset;
   const uint32_t bar_kv = bars, bar_q0 = bars + 8, bar_do = bars + 24, bar_sdp = bars + 32, bar_pds = bars + 40,
-                 bar_dv = bars + 48, bar_dq = bars + 56, bar_free = bars + 64;   // bar_q0 + 8: second Q buffer
+                 bar_dv = bars + 48, bar_dq = bars + 56, bar_free = bars + 64, bar_pfree = bars + 72;   // bar_q0 + 8: second Q buffer
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kBarOffset + L::kNumBars * 8 + 4);
 
@@ -127,6 +127,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     mbar_init(bar_do, 1);
     mbar_init(bar_dv, 1);
     mbar_init(bar_sdp, 1);
+    mbar_init(bar_pfree, 1);
     mbar_init(bar_pds, kBwdComputeThreads);
     mbar_init(bar_dq, 1);
     mbar_init(bar_free, kBwdComputeThreads);
@@ -231,16 +232,28 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         const uint64_t off = (uint64_t)(((ks / 4) * L::kPanel + (ks % 4) * 32) >> 4);
         mma_ss(tDP, d_do + off, d_v + off, kIdSS, ks > 0, issue);
       }
-      // the first half of the previous pair's dQ tile must have left the P bytes before
-      // they are rewritten (the second half sits in a Q buffer and may still be on its way)
-      if (issue) bulk_wait_read_but_one();
-      __syncwarp();
       mma_commit(bar_sdp, issue);
+      // the first half of the previous pair's dQ tile must have left the P bytes before
+      // they are rewritten (the second half sits in a Q buffer and may still be on its way);
+      // told to the compute warps separately, so that they wait for it only when they are
+      // about to store, after their exponentials
+      if (issue) { bulk_wait_read_but_one(); mbar_arrive(bar_pfree); }
+      __syncwarp();
       // wait for P and dS in shared memory
       mbar_wait(bar_pds, it & 1, abort_flag);
       tc_fence_after();
+      const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+      for (int ks = 0; ks < kT / 16; ++ks) {   // contraction over the 128 queries
+        const uint64_t off = (uint64_t)((ks * 2048) >> 4);
+        mma_ss(tDV, d_p_mn + off, d_do_mn + off, kIdTT, ks > 0 ? 1u : acc, issue);
+      }
+      mma_commit(bar_dv, issue);
+      // (issued first and alone: the loader refetches dO the moment this product has read it, and
+      // that fetch is the longest wait of a pair)
       // The Q buffer of pair it - 1 held the second half of its dQ tile; once that is
-      // read it takes the query tile of pair it + 1 (in L2 by now).
+      // read it takes the query tile of pair it + 1 (in L2 by now).  Behind the dV issue: waiting
+      // for the copy engine here must not delay the product that frees dO.
       if (it > 0 && it + 1 < n_iter) {
         int in, hqn;
         pair_of(it + 1, in, hqn);
@@ -253,13 +266,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         }
         __syncwarp();
       }
-      const uint32_t acc = it > 0 ? 1u : 0u;
-#pragma unroll
-      for (int ks = 0; ks < kT / 16; ++ks) {   // contraction over the 128 queries
-        const uint64_t off = (uint64_t)((ks * 2048) >> 4);
-        mma_ss(tDV, d_p_mn + off, d_do_mn + off, kIdTT, ks > 0 ? 1u : acc, issue);
-      }
-      mma_commit(bar_dv, issue);
 #pragma unroll
       for (int ks = 0; ks < kT / 16; ++ks) {
         const uint64_t off = (uint64_t)((ks * 2048) >> 4);
@@ -310,21 +316,30 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     uint8_t* sP = sgen + L::kP;
     uint8_t* sDS = sgen + L::kDS;
-    for (int it = 0; it < n_iter; ++it) {
-      const int g = it % p.group, i = i_first + it / p.group;
-      const int hq = hk * p.group + g;
-      const int qi = i * kT + row;
-      const bool row_ok = qi < len;
-      const long long tok = (long long)seq_start + qi;
-      float lse2 = 0.f, dsum = 0.f;
-      bool live = false;
-      if (row_ok) {
-        const float l = p.lse[(p.cu_seqlens ? 0 : (long long)b * p.lse_sb) + tok * p.lse_st + (long long)hq * p.lse_sh];
-        lse2 = p.lse_base2 ? l : l * 1.4426950408889634f;
-        live = l != -INFINITY;
-        const long long tl = p.cu_seqlens ? tok : (long long)b * p.seqlen + qi;
-        dsum = p.dvec[tl * p.heads_q + hq];
+    // lse and D of a pair's rows are fetched a pair ahead (global loads take thousands of cycles
+    // while the reduce-adds keep the L2 busy)
+    float lse2_nx = 0.f, dsum_nx = 0.f;
+    bool live_nx = false;
+    auto fetch_row_stats = [&](int itx) {
+      lse2_nx = 0.f; dsum_nx = 0.f; live_nx = false;
+      if (itx >= n_iter) return;
+      const int gx = itx % p.group, ix = i_first + itx / p.group;
+      const int hqx = hk * p.group + gx, qix = ix * kT + row;
+      if (qix < len) {
+        const long long tokx = (long long)seq_start + qix;
+        const float l = p.lse[(p.cu_seqlens ? 0 : (long long)b * p.lse_sb) + tokx * p.lse_st + (long long)hqx * p.lse_sh];
+        lse2_nx = p.lse_base2 ? l : l * 1.4426950408889634f;
+        live_nx = l != -INFINITY;
+        const long long tl = p.cu_seqlens ? tokx : (long long)b * p.seqlen + qix;
+        dsum_nx = p.dvec[tl * p.heads_q + hqx];
       }
+    };
+    fetch_row_stats(0);
+    for (int it = 0; it < n_iter; ++it) {
+      const int i = i_first + it / p.group;
+      const int qi = i * kT + row;
+      const float lse2 = lse2_nx, dsum = dsum_nx;
+      const bool live = live_nx;
       mbar_wait(bar_sdp, it & 1, abort_flag);
       tc_fence_after();
       // visible keys of this row inside the tile: columns [0, lim)
@@ -354,6 +369,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
           dd[x / 2] = pack2<T>(d0, d1);
         }
         // row `row` of a [128 q][128 k] tile, two 64-column panels, 128-byte swizzle
+        if (c2 == 0) mbar_wait(bar_pfree, it & 1, abort_flag);      // the P tile is no longer being read out
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           const int chunk = 4 * cc + ch;                       // 16-byte chunk of the 256-byte row
@@ -365,6 +381,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       fence_proxy_async();       // generic-proxy writes -> visible to the tensor core's reads
       tc_fence_before();
       mbar_arrive(bar_pds);
+      fetch_row_stats(it + 1);
       // dQ tile of this pair -> fp32 accumulator
       mbar_wait(bar_dq, it & 1, abort_flag);
       tc_fence_after();
