@@ -450,25 +450,37 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
 }
 
 
-// D[t, h] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head).
+// D[t, h] = sum_d dO[t, h, d] * O[t, h, d], and the row's fp32 dQ accumulator cleared (saves a
+// separate memset pass over it): eight lanes per (token, head) with 16-byte loads.
 template <typename T>
 __global__ void bwd_rowsum_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ dvec,
-                                  long long o_sb, long long o_st, long long o_sh, long long do_sb,
-                                  long long do_st, long long do_sh, int tokens_per_batch, int heads, int D,
-                                  long long total) {
-  const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (idx >= total) return;
-  const int lane = threadIdx.x & 31;
-  const int hq = (int)(idx % heads);
-  const long long tl = idx / heads;
-  const long long bb = tl / tokens_per_batch, tt = tl % tokens_per_batch;
-  const T* orow = o + bb * o_sb + tt * o_st + (long long)hq * o_sh;
-  const T* drow = d_o + bb * do_sb + tt * do_st + (long long)hq * do_sh;
+                                  float* __restrict__ dq_acc, long long o_sb, long long o_st, long long o_sh,
+                                  long long do_sb, long long do_st, long long do_sh, int tokens_per_batch, int heads,
+                                  int D, int DP, long long total) {
+  const int sub = threadIdx.x & 7;
+  const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
   float s = 0.f;
-  for (int d = lane; d < D; d += 32) s += (float)orow[d] * (float)drow[d];
+  if (idx < total) {
+    const int hq = (int)(idx % heads);
+    const long long tl = idx / heads;
+    const long long bb = tl / tokens_per_batch, tt = tl % tokens_per_batch;
+    const T* orow = o + bb * o_sb + tt * o_st + (long long)hq * o_sh;
+    const T* drow = d_o + bb * do_sb + tt * do_st + (long long)hq * do_sh;
+    for (int c = 8 * sub; c < D; c += 64) {
+      const uint4 ov = *reinterpret_cast<const uint4*>(orow + c);
+      const uint4 dv = *reinterpret_cast<const uint4*>(drow + c);
+      const T* oe = reinterpret_cast<const T*>(&ov);
+      const T* de = reinterpret_cast<const T*>(&dv);
 #pragma unroll
-  for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(0xffffffffu, s, k);
-  if (lane == 0) dvec[idx] = s;
+      for (int x = 0; x < 8; ++x) s = fmaf((float)oe[x], (float)de[x], s);
+    }
+    float4* acc = reinterpret_cast<float4*>(dq_acc + idx * DP);
+    for (int c = sub; c < DP / 4; c += 8) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  if (idx < total && sub == 0) dvec[idx] = s;
 }
 
 // dq[t, h, :D] = T(dq_acc[t, h, :D])
@@ -590,17 +602,15 @@ int launch_bwd(const b200attn_prefill_bwd_args* a, const BwdParams& p, cudaStrea
   CUtensorMap tdq;
   if (!make_dq_tmap(&tdq, p.dq_acc, DP, rows / a->heads_q, a->heads_q)) return B200ATTN_ERR_CUDA;
   const int tpb = a->cu_seqlens ? (int)a->total_tokens : a->seqlen;   // tokens per batch entry of the dense index
-  // 1. D = rowsum(dO o O)
+  // 1. D = rowsum(dO o O), and the dq accumulator cleared
   {
-    const int warps_per_block = 8;
-    const long long blocks = (rows + warps_per_block - 1) / warps_per_block;
-    bwd_rowsum_kernel<T><<<(unsigned)blocks, warps_per_block * 32, 0, stream>>>(
-        (const T*)a->o, (const T*)a->d_o, const_cast<float*>(p.dvec), a->cu_seqlens ? 0 : a->o_stride_b,
+    const long long blocks = (rows * 8 + 255) / 256;
+    bwd_rowsum_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
+        (const T*)a->o, (const T*)a->d_o, const_cast<float*>(p.dvec), p.dq_acc, a->cu_seqlens ? 0 : a->o_stride_b,
         a->o_stride_t, a->o_stride_h, a->cu_seqlens ? 0 : a->do_stride_b, a->do_stride_t, a->do_stride_h, tpb,
-        a->heads_q, a->head_dim, rows);
+        a->heads_q, a->head_dim, DP, rows);
   }
-  // 2. main kernel (dq accumulator zeroed first)
-  if (cudaMemsetAsync(p.dq_acc, 0, (size_t)rows * DP * 4, stream) != cudaSuccess) return B200ATTN_ERR_CUDA;
+  // 2. main kernel (the dq accumulator was cleared by the row-sum kernel)
   dim3 grid(p.n_kvtiles, a->heads_kv, a->batch);
   kern<<<grid, kBwdThreads, L::kAlloc, stream>>>(tq, tk, tv, tdo, tdq, p);
   // 3. dq accumulator -> dq
