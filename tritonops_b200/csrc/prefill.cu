@@ -560,12 +560,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           const bool has1 = 2 * j + 1 < n_u[t];
           const int u1 = has1 ? ulist(t, 2 * j + 1) : 0;
           const unsigned f0 = uflags(t, 2 * j), f1 = has1 ? uflags(t, 2 * j + 1) : 0u;
-          bool full = has1 && f0 == 3u && f1 == 3u && (u1 + 1) * kBlk <= len && (u0 + 1) * kBlk <= len;
-          if (p.causal) full = full && (u1 + 1) * kBlk - 1 <= q0t && (u0 + 1) * kBlk - 1 <= q0t;
           const int qa = row >> 6;                 // query block inside the tile (uniform per warp)
           vis0 = (f0 >> qa) & 1u;
           vis1 = (f1 >> qa) & 1u;
-          if (!full) {
+          // A half this warp's query block does not list is skipped below (no maximum, no
+          // exponentials, P = 0), so only a listed half that the sequence end or the causal
+          // diagonal cuts for some row of this warp needs the element mask: with random lists
+          // most steps hold a block of one of the two query blocks only, and none of them does.
+          const int q_lo = q0t + 32 * (warp & 3);  // first query row of this warp
+          const bool cut0 = vis0 && ((u0 + 1) * kBlk > len || (p.causal && (u0 + 1) * kBlk - 1 > q_lo));
+          const bool cut1 = vis1 && ((u1 + 1) * kBlk > len || (p.causal && (u1 + 1) * kBlk - 1 > q_lo));
+          if (cut0 || cut1) {
             int lim0 = vis0 ? min(kBlk, len - u0 * kBlk) : 0;
             int lim1 = vis1 ? min(kBlk, len - u1 * kBlk) : 0;
             if (p.causal) { lim0 = min(lim0, qi - u0 * kBlk + 1); lim1 = min(lim1, qi - u1 * kBlk + 1); }
