@@ -6,7 +6,7 @@
 //   dx_td = r_t (w_d dy_td - x_td r_t^2 mean_d'(dy_td' w_d' x_td'))
 //   dw_d  = sum_t dy_td x_td r_t
 //
-// Large inputs (1024 rows or more of 2 .. 16 KB) take the streaming kernels: persistent CTAs
+// Large inputs (1024 rows or more of 2 .. 12 KB) take the streaming kernels: persistent CTAs
 // whose producer warp feeds a shared-memory ring with bulk copies.  Otherwise -- forward: one
 // warp per row, two passes over the row (the second one hits L1), 16-byte loads when the row
 // is aligned for them; backward: a fixed number of CTAs each walk rows c, c + G, ....  In every
@@ -140,7 +140,7 @@ rmsnorm_fwd_reg_kernel(const XT* __restrict__ x, const WT* __restrict__ w, XT* _
 }
 
 // ---------------------------------------------------------------------------
-// Streaming kernels for rows of 2 .. 16 KB: one persistent CTA per SM.  A producer warp brings
+// Streaming kernels for rows of 2 .. 12 KB (forward) / 2 .. 13.5 KB (backward): one persistent CTA per SM.  A producer warp brings
 // the CTA's rows (blockIdx.x, blockIdx.x + gridDim.x, ...) one per slot into a 192 KB ring with
 // untiled bulk copies, so the bytes in flight per SM are set by the ring instead of by how many
 // loads the resident warps have outstanding; consumer warps take the rows in turn from shared
@@ -154,7 +154,10 @@ rmsnorm_fwd_reg_kernel(const XT* __restrict__ x, const WT* __restrict__ w, XT* _
 // of order, so the row in between, another consumer's, may still be in flight).  Hence a
 // consumer first waits until the slot's previous row has been released (the same wait the
 // producer does before refilling it) and only then for its own row: from that point the only
-// phase the slot's full barrier can complete is this row's.
+// phase the slot's full barrier can complete is this row's.  (That first wait is itself free of
+// aliasing because the producer issues rows in order and the ring has at least as many slots as
+// there are consumers: a consumer's previous row having landed implies that the row before this
+// one in the slot had been issued, hence that the one before that had been released.)
 // ---------------------------------------------------------------------------
 constexpr int kRingBytes = 192 * 1024;
 constexpr int kMaxSlots = 96;
@@ -613,9 +616,13 @@ int launch_fwd(const b200attn_rmsnorm_fwd_args* a, cudaStream_t stream) {
                    ((uintptr_t)a->x & 15) == 0 && ((uintptr_t)a->y & 15) == 0 && ((uintptr_t)a->weight & 15) == 0;
   const long long ctas = (a->rows + kFwdWarps - 1) / kFwdWarps;
   if (ctas > 0x7fffffffLL) return B200ATTN_ERR_TOO_LARGE;
-  // rows of 2 .. 16 KB, enough of them to fill the machine: the streaming kernel
+  // rows of 2 .. 12 KB, enough of them to fill the machine: the streaming kernel
   const long long row_bytes = (long long)a->dim * (long long)sizeof(XT);
-  if (vec && row_bytes >= 2048 && row_bytes <= 16384 && a->dim * 4 <= 32768 && a->rows >= 1024) {
+  // (the ring must have a slot per consumer warp at least: the release-then-landing wait of the
+  // consumers is only free of phase aliasing if the producer, which works in row order, cannot be
+  // a whole ring behind a consumer's previous row)
+  if (vec && row_bytes >= 2048 && kRingBytes / ((row_bytes + 127) & ~127LL) >= kFwdStreamConsumers &&
+      a->dim * 4 <= 32768 && a->rows >= 1024) {
     const DeviceInfo* di = nullptr;
     if (int st = device_info(&di)) return st;
     const int slot = (int)((row_bytes + 127) & ~127LL);
@@ -661,8 +668,10 @@ int launch_bwd_rms(const b200attn_rmsnorm_bwd_args* a, cudaStream_t stream) {
   // rows of at least 2 KB, at most 4096 columns (the dw sums of a row live in one warp's registers)
   const long long row_bytes = (long long)a->dim * (long long)sizeof(XT);
   const int ch = (a->dim / N + 63) / 64;                      // 16-byte chunks per lane (two warps share a row)
-  if (vec && ((uintptr_t)a->weight & 15) == 0 && row_bytes >= 2048 && row_bytes <= 16384 && a->dim <= 4096 &&
-      ch <= (N == 4 ? 16 : 8) && a->rows >= 1024) {
+  // (and a ring slot per pair of consumer warps at least, see the forward)
+  if (vec && ((uintptr_t)a->weight & 15) == 0 && row_bytes >= 2048 &&
+      kRingBytes / (2 * ((row_bytes + 127) & ~127LL)) >= kBwdPairs && a->dim <= 4096 && ch <= (N == 4 ? 16 : 8) &&
+      a->rows >= 1024) {
     const DeviceInfo* di = nullptr;
     if (int st = device_info(&di)) return st;
     const int grid = di->sm_count < g ? di->sm_count : g;     // partial rows: the workspace holds g of them
