@@ -53,8 +53,31 @@ struct BwdParams {
   int causal;
   float scale_log2, scale;   // q.k multiplier in base-2 and natural form
   int lse_base2;
+  int prefetch_ahead;        // CTAs resident at once: a CTA asks for the first tiles of CTA + this into L2
   int* status_word;
 };
+
+// (sequence, KV head) pairs are taken in groups of kBwdHeadGroup: inside a group the key tiles
+// with the most query tiles to visit (the first ones when causal) of all its heads come first,
+// which keeps the tail of the launch short, and the group is small enough for its fp32 dQ
+// accumulators (the target of every reduce-add) to stay in L2 while its CTAs are resident.
+#ifndef B200ATTN_BWD_HEAD_GROUP
+#define B200ATTN_BWD_HEAD_GROUP 8
+#endif
+constexpr int kBwdHeadGroup = B200ATTN_BWD_HEAD_GROUP;
+struct BwdCta { int jt, hk, b; };
+__device__ __forceinline__ BwdCta bwd_cta_of(const BwdParams& p, int bid) {
+  const int n_bh = p.batch * p.heads_kv;
+  const int per_group = kBwdHeadGroup * p.n_kvtiles;
+  const int grp = bid / per_group, in_grp = bid - grp * per_group;
+  const int g_heads = min(kBwdHeadGroup, n_bh - grp * kBwdHeadGroup);
+  const int bh = grp * kBwdHeadGroup + in_grp % g_heads;
+  BwdCta c;
+  c.jt = in_grp / g_heads;
+  c.hk = bh % p.heads_kv;
+  c.b = bh / p.heads_kv;
+  return c;
+}
 
 __device__ __forceinline__ float ex2f(float x) {
   float y;
@@ -94,8 +117,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
   constexpr uint32_t kIdDQ = idesc_f16(kFmt, true, kT, DP, false);     // dQ: A K-major, B MN-major
   constexpr int kPanels = DP / 64;
 
-  const int jt = blockIdx.x;                 // key tile
-  const int hk = blockIdx.y, b = blockIdx.z;
+  const BwdCta me = bwd_cta_of(p, blockIdx.x);
+  const int jt = me.jt;                      // key tile
+  const int hk = me.hk, b = me.b;
   int seq_start = 0, len = p.seqlen, bcoord = b;
   if (p.cu_seqlens) {
     seq_start = p.cu_seqlens[b];
@@ -165,6 +189,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         mbar_expect_tx(bar, L::kOperand);
         for (int pn = 0; pn < kPanels; ++pn)
           tma_load_4d(dst + pn * L::kPanel, &tmap_q, bar, 64 * pn, seq_start + i * kT, hq, bcoord);
+      }
+      // The CTA that will start when one of the resident ones ends finds its K / V tile and its
+      // first Q / dO tiles on their way into L2.
+      if (p.prefetch_ahead > 0 && blockIdx.x + p.prefetch_ahead < gridDim.x) {
+        const BwdCta nx = bwd_cta_of(p, blockIdx.x + p.prefetch_ahead);
+        int ss2 = 0, len2 = p.seqlen, bc2 = nx.b;
+        if (p.cu_seqlens) { ss2 = p.cu_seqlens[nx.b]; len2 = min(p.cu_seqlens[nx.b + 1] - ss2, p.n_kvtiles * kT); bc2 = 0; }
+        if (nx.jt * kT < len2) {
+          const int i2 = p.causal ? nx.jt : 0, hq2 = nx.hk * p.group;
+          for (int pn = 0; pn < kPanels; ++pn) {
+            tma_prefetch_4d(&tmap_k, 64 * pn, ss2 + nx.jt * kT, nx.hk, bc2);
+            tma_prefetch_4d(&tmap_v, 64 * pn, ss2 + nx.jt * kT, nx.hk, bc2);
+            tma_prefetch_4d(&tmap_q, 64 * pn, ss2 + i2 * kT, hq2, bc2);
+            tma_prefetch_4d(&tmap_do, 64 * pn, ss2 + i2 * kT, hq2, bc2);
+          }
+        }
       }
       for (int it = 0; it < n_iter; ++it) {
         int i, hq;
@@ -305,7 +345,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       }
       __syncwarp();
     }
+#ifdef B200ATTN_BWD_READ_WAIT
+    if (issue) bulk_wait_read_all();
+#else
     if (issue) bulk_wait_all();
+#endif
     __syncwarp();
   } else if (warp < kBwdComputeWarps) {
     // ============================================ compute warps: two threads per row
@@ -611,7 +655,9 @@ int launch_bwd(const b200attn_prefill_bwd_args* a, const BwdParams& p, cudaStrea
         a->heads_q, a->head_dim, DP, rows);
   }
   // 2. main kernel (the dq accumulator was cleared by the row-sum kernel)
-  dim3 grid(p.n_kvtiles, a->heads_kv, a->batch);
+  const long long n_ctas = (long long)p.n_kvtiles * a->heads_kv * a->batch;
+  if (n_ctas > 0x7fffffffLL) return B200ATTN_ERR_TOO_LARGE;
+  dim3 grid((unsigned)n_ctas);
   kern<<<grid, kBwdThreads, L::kAlloc, stream>>>(tq, tk, tv, tdo, tdq, p);
   // 3. dq accumulator -> dq
   {
@@ -639,7 +685,8 @@ int prefill_bwd(const b200attn_prefill_bwd_args* a, cudaStream_t stream) {
   const size_t need = prefill_bwd_workspace_bytes(a);
   if (!a->workspace || a->workspace_bytes < need) return B200ATTN_ERR_WORKSPACE;
   if ((uintptr_t)a->workspace & 15) return B200ATTN_ERR_ALIGN;
-  st = device_info(nullptr);
+  const DeviceInfo* di = nullptr;
+  st = device_info(&di);
   if (st != B200ATTN_OK) return st;
   const long long rows = total_rows(a);
   const int DP = dpad(a->head_dim);
@@ -663,6 +710,7 @@ int prefill_bwd(const b200attn_prefill_bwd_args* a, cudaStream_t stream) {
   p.scale_log2 = a->softmax_scale * (a->scale_has_log2e ? 1.f : 1.4426950408889634f);
   p.lse_base2 = a->lse_base2;
   p.status_word = a->status_word;
+  p.prefetch_ahead = di->sm_count;   // one CTA per SM
   const bool dp64 = DP == 64;
   if (a->dtype == B200ATTN_F16)
     return dp64 ? launch_bwd<__half, 64>(a, p, stream) : launch_bwd<__half, 128>(a, p, stream);

@@ -245,6 +245,17 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_
   return d;
 }
 
+// 16 consecutive 32-bit columns of this thread's TMEM lane <- registers.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15])
+      : "memory");
+}
+
 // Instruction descriptor for kind::f16: fp32 accumulate, A and B both `fmt`
 // (0 = f16, 1 = bf16), A K-major, B K-major or MN-major, M x N tile.
 __host__ __device__ constexpr uint32_t idesc_f16(uint32_t fmt, bool b_mn_major, uint32_t M,
