@@ -12,16 +12,18 @@
 // dK and dV of the tile accumulate in tensor memory across that whole walk
 // (which also sums the group's query heads, done on the host in the
 // reference, :813), dQ tiles are added to an fp32 accumulator in global memory
-// with vector reductions and converted at the end.  All five products are
-// tcgen05.mma: S and dP with both operands K-major from shared memory; P and
-// dS are written by the softmax threads into 128-byte-swizzled shared memory
-// once and read twice, as the MN-major A operand of dV / dK and as the K-major
-// A operand of dQ.  TMEM columns: S [0,128), dP then dQ [128,256), dK
-// [256,384), dV [384,512).  Pipelining across (query tile, key tile) pairs: the
-// query tiles are double buffered and the next pair's S is issued right behind
-// this pair's dQ; dO is refetched as soon as the dV product has read it (and asked
-// into L2 a pair ahead); the fp32 dQ tile leaves through shared memory and a copy-
-// engine reduce-add, which runs while the next pair is computed.
+// by the copy engine and converted at the end.  All five products are
+// tcgen05.mma.  The scores are formed transposed, S^T = K Q^T and dP^T = V dO^T
+// (keys on the TMEM lanes), so that P^T and dS^T, written back over them as
+// 16-bit, are the A operands of dV and dK straight from tensor memory; only
+// dS^T also goes to shared memory ([key][query], 128-byte swizzle), where
+// dQ = dS K reads it as an MN-major A operand.  TMEM columns: S^T [0,128) with
+// P^T in [0,32) and [64,96), dP^T then dQ [128,256) with dS^T in [128,160) and
+// [192,224), dK [256,384), dV [384,512).  Pipelining across (query tile, key
+// tile) pairs: Q and dO tiles are double buffered (a dO fetch takes ~3000 cycles
+// while the reduce-adds keep the L2 busy), the next pair's S^T is issued right
+// behind this pair's dQ, and the fp32 dQ tile leaves through shared memory and a
+// copy-engine reduce-add that runs while the next pair is computed.
 #include <type_traits>
 
 #include "common.cuh"
@@ -90,19 +92,21 @@ template <int DP>
 struct BwdSmem {
   static constexpr int kOperand = kT * DP * 2;       // K, V, Q, dO tiles
   static constexpr int kPanel = kT * 128;            // one 64-column swizzled panel
-  static constexpr int kPds = kT * kT * 2;           // P, dS tiles
-  static constexpr int kK = 0, kV = kOperand, kQ = 2 * kOperand, kDO = 3 * kOperand;
-  static constexpr int kP = 4 * kOperand, kDS = kP + kPds;
-  static constexpr int kQ1 = kDS + kPds;             // second Q tile (query tiles are double buffered)
+  static constexpr int kPds = kT * kT * 2;           // dS^T tile
+  static constexpr int kK = 0, kV = kOperand, kQ = 2 * kOperand, kQ1 = 3 * kOperand;   // Q and dO: two buffers each
+  static constexpr int kDO = 4 * kOperand, kDO1 = 5 * kOperand;
+  static constexpr int kDS = 6 * kOperand;
   // The fp32 dQ tile leaves through shared memory in panels of 32 columns (128 rows,
-  // 128-byte swizzle): the first half of the panels in the P tile, the second half in
+  // 128-byte swizzle): the first half of the panels in the dS^T tile, the second half in
   // the pair's own Q buffer, both dead by the time dQ exists.
   static constexpr int kStagePanel = kT * 128;
   static_assert((DP / 64) * kStagePanel <= kPds && (DP / 64) * kStagePanel <= kOperand, "dQ staging fits");
-  static constexpr int kBarOffset = kQ1 + kOperand;
-  static constexpr int kNumBars = 10;
+  static constexpr int kStats = kDS + kPds;          // (lse2, D) of the pair's 128 query rows
+  static constexpr int kBarOffset = kStats + kT * 8;
+  static constexpr int kNumBars = 13;
   static constexpr int kBytes = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kAlloc = kBytes + 1024;
+  static_assert(kAlloc <= 232448, "shared memory of one CTA");
 };
 
 template <typename T, int DP>
@@ -112,9 +116,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
            const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
   using L = BwdSmem<DP>;
   constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-  constexpr uint32_t kIdSS = idesc_f16(kFmt, false, kT, kT);           // S, dP: A, B K-major
-  constexpr uint32_t kIdTT = idesc_f16(kFmt, true, kT, DP, true);      // dV, dK: A, B MN-major
-  constexpr uint32_t kIdDQ = idesc_f16(kFmt, true, kT, DP, false);     // dQ: A K-major, B MN-major
+  constexpr uint32_t kIdSS = idesc_f16(kFmt, false, kT, kT);           // S^T, dP^T: A, B K-major
+  constexpr uint32_t kIdTS = idesc_f16(kFmt, true, kT, DP, false);     // dV, dK: A from tensor memory, B MN-major
+  constexpr uint32_t kIdDQ = idesc_f16(kFmt, true, kT, DP, true);      // dQ: A, B MN-major
   constexpr int kPanels = DP / 64;
 
   const BwdCta me = bwd_cta_of(p, blockIdx.x);
@@ -137,8 +141,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t bars = sbase + L::kBarOffset;
-  const uint32_t bar_kv = bars, bar_q0 = bars + 8, bar_do = bars + 24, bar_sdp = bars + 32, bar_pds = bars + 40,
-                 bar_dv = bars + 48, bar_dq = bars + 56, bar_free = bars + 64, bar_pfree = bars + 72;   // bar_q0 + 8: second Q buffer
+  const uint32_t bar_kv = bars, bar_q0 = bars + 8 /* +16: second buffer */, bar_do0 = bars + 24 /* +32 */,
+                 bar_s = bars + 40, bar_dp = bars + 48, bar_pds = bars + 56, bar_dv0 = bars + 64 /* +72 */,
+                 bar_dq = bars + 80, bar_free = bars + 88, bar_pfree = bars + 96;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kBarOffset + L::kNumBars * 8 + 4);
 
@@ -148,9 +153,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     mbar_init(bar_kv, 1);
     mbar_init(bar_q0, 1);
     mbar_init(bar_q0 + 8, 1);
-    mbar_init(bar_do, 1);
-    mbar_init(bar_dv, 1);
-    mbar_init(bar_sdp, 1);
+    mbar_init(bar_do0, 1);
+    mbar_init(bar_do0 + 8, 1);
+    mbar_init(bar_dv0, 1);
+    mbar_init(bar_dv0 + 8, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_dp, 1);
     mbar_init(bar_pfree, 1);
     mbar_init(bar_pds, kBwdComputeThreads);
     mbar_init(bar_dq, 1);
@@ -168,28 +176,41 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tDP = tmem + 128, tDK = tmem + 256, tDV = tmem + 384;
+  // P^T / dS^T of the 16 queries of contraction step ks, as written by the compute warps:
+  // queries [64 h, 64 h + 64) of a key row are packed into columns [64 h, 64 h + 32)
+  auto a_cols = [](int ks) -> uint32_t { return (uint32_t)(64 * (ks / 4) + 8 * (ks % 4)); };
 
   // query tile and head of pair `it`
   auto pair_of = [&](int it, int& i, int& hq) { i = i_first + it / p.group; hq = hk * p.group + it % p.group; };
   if (warp == kBwdLoadWarp) {
-    // ============================================ loader warp: K, V, the first Q tiles, every dO tile
-    // (dO has one buffer: pair it + 1's tile is fetched the moment the dV product of
-    // pair it has read it, which must not wait for the MMA warp to finish issuing)
+    // ============================================ loader warp: every load, and the dQ reduce-adds
     if (elect_one()) {
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
-      mbar_expect_tx(bar_kv, 2 * L::kOperand);
-      for (int pn = 0; pn < kPanels; ++pn) {
-        tma_load_4d(sbase + L::kK + pn * L::kPanel, &tmap_k, bar_kv, 64 * pn, seq_start + kv0, hk, bcoord);
-        tma_load_4d(sbase + L::kV + pn * L::kPanel, &tmap_v, bar_kv, 64 * pn, seq_start + kv0, hk, bcoord);
-      }
-      for (int it = 0; it < min(n_iter, 2); ++it) {
+      auto load_do = [&](int it) {
         int i, hq;
         pair_of(it, i, hq);
-        const uint32_t dst = sbase + (it ? L::kQ1 : L::kQ), bar = bar_q0 + 8 * it;
+        const uint32_t dst = sbase + ((it & 1) ? L::kDO1 : L::kDO), bar = bar_do0 + 8 * (it & 1);
+        mbar_expect_tx(bar, L::kOperand);
+        for (int pn = 0; pn < kPanels; ++pn)
+          tma_load_4d(dst + pn * L::kPanel, &tmap_do, bar, 64 * pn, seq_start + i * kT, hq, bcoord);
+      };
+      auto load_q = [&](int it) {
+        int i, hq;
+        pair_of(it, i, hq);
+        const uint32_t dst = sbase + ((it & 1) ? L::kQ1 : L::kQ), bar = bar_q0 + 8 * (it & 1);
         mbar_expect_tx(bar, L::kOperand);
         for (int pn = 0; pn < kPanels; ++pn)
           tma_load_4d(dst + pn * L::kPanel, &tmap_q, bar, 64 * pn, seq_start + i * kT, hq, bcoord);
-      }
+      };
+      // in the order the first products need them: K and Q(0) for S^T, V and dO(0) for dP^T
+      mbar_expect_tx(bar_kv, 2 * L::kOperand);
+      for (int pn = 0; pn < kPanels; ++pn)
+        tma_load_4d(sbase + L::kK + pn * L::kPanel, &tmap_k, bar_kv, 64 * pn, seq_start + kv0, hk, bcoord);
+      load_q(0);
+      for (int pn = 0; pn < kPanels; ++pn)
+        tma_load_4d(sbase + L::kV + pn * L::kPanel, &tmap_v, bar_kv, 64 * pn, seq_start + kv0, hk, bcoord);
+      load_do(0);
+      if (n_iter > 1) { load_q(1); load_do(1); }
       // The CTA that will start when one of the resident ones ends finds its K / V tile and its
       // first Q / dO tiles on their way into L2.
       if (p.prefetch_ahead > 0 && blockIdx.x + p.prefetch_ahead < gridDim.x) {
@@ -200,126 +221,129 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
           const int i2 = p.causal ? nx.jt : 0, hq2 = nx.hk * p.group;
           for (int pn = 0; pn < kPanels; ++pn) {
             tma_prefetch_4d(&tmap_k, 64 * pn, ss2 + nx.jt * kT, nx.hk, bc2);
-            tma_prefetch_4d(&tmap_v, 64 * pn, ss2 + nx.jt * kT, nx.hk, bc2);
             tma_prefetch_4d(&tmap_q, 64 * pn, ss2 + i2 * kT, hq2, bc2);
+            tma_prefetch_4d(&tmap_v, 64 * pn, ss2 + nx.jt * kT, nx.hk, bc2);
             tma_prefetch_4d(&tmap_do, 64 * pn, ss2 + i2 * kT, hq2, bc2);
           }
         }
       }
+      // Per pair: the dO tile two pairs ahead (into the buffer this pair's dV product frees), the
+      // pair's dQ tile added to the fp32 accumulator in global memory once the compute warps have
+      // staged it (first half of the columns in the dS^T tile, second half in the pair's Q buffer,
+      // one bulk group each; rows past the sequence end hold exact zeros), and the Q tile two pairs
+      // ahead into that Q buffer once the copy engine has read it.  All of it here and not in the
+      // MMA warp: issuing the reduce-adds alone blocks for ~1000 cycles while the engine is busy.
+      mbar_arrive(bar_pfree);         // nothing is being read out of the dS^T tile before the first pair
       for (int it = 0; it < n_iter; ++it) {
         int i, hq;
         pair_of(it, i, hq);
-        if (it > 0) mbar_wait(bar_dv, (it - 1) & 1, abort_flag);
-        mbar_expect_tx(bar_do, L::kOperand);
-        for (int pn = 0; pn < kPanels; ++pn)
-          tma_load_4d(sbase + L::kDO + pn * L::kPanel, &tmap_do, bar_do, 64 * pn, seq_start + i * kT, hq, bcoord);
-        if (it + 1 < n_iter) {        // next pair's dO, and the Q tile after next, into L2
-          int in, hqn;
-          pair_of(it + 1, in, hqn);
-          for (int pn = 0; pn < kPanels; ++pn) tma_prefetch_4d(&tmap_do, 64 * pn, seq_start + in * kT, hqn, bcoord);
-          if (it + 2 < n_iter) {
-            pair_of(it + 2, in, hqn);
-            for (int pn = 0; pn < kPanels; ++pn) tma_prefetch_4d(&tmap_q, 64 * pn, seq_start + in * kT, hqn, bcoord);
+        if (it + 2 < n_iter) {
+          if (it + 3 < n_iter) {      // the pair after that into L2
+            int in, hqn;
+            pair_of(it + 3, in, hqn);
+            for (int pn = 0; pn < kPanels; ++pn) {
+              tma_prefetch_4d(&tmap_do, 64 * pn, seq_start + in * kT, hqn, bcoord);
+              tma_prefetch_4d(&tmap_q, 64 * pn, seq_start + in * kT, hqn, bcoord);
+            }
           }
+          // (one barrier per dO buffer: the product that completes it again cannot run before the
+          // load below, so the phase waited for here is never more than one behind)
+          if (!mbar_wait(bar_dv0 + 8 * (it & 1), (it >> 1) & 1, abort_flag)) break;
+          load_do(it + 2);
+        }
+        if (!mbar_wait(bar_free, it & 1, abort_flag)) break;
+        const int tl0 = (p.cu_seqlens ? seq_start : b * p.seqlen) + i * kT;
+        const uint32_t q_off = (it & 1) ? L::kQ1 : L::kQ;
+        for (int pn = 0; pn < DP / 64; ++pn)
+          tma_reduce_add_3d(&tmap_dq, sbase + L::kDS + pn * L::kStagePanel, 32 * pn, tl0, hq);
+        bulk_commit_group();
+        for (int pn = 0; pn < DP / 64; ++pn)
+          tma_reduce_add_3d(&tmap_dq, sbase + q_off + pn * L::kStagePanel, 32 * (DP / 64 + pn), tl0, hq);
+        bulk_commit_group();
+        bulk_wait_read_but_one();     // the dS^T tile may be rewritten (the next pair's compute warps wait for this)
+        mbar_arrive(bar_pfree);
+        if (it + 2 < n_iter) {
+          bulk_wait_read_all();       // and the Q buffer refilled
+          load_q(it + 2);
         }
       }
+      bulk_wait_all();
     }
     __syncwarp();
   } else if (warp == kBwdCtrlWarp) {
-    // ============================================ MMA warp: products, Q reloads, dQ reduce-adds
+    // ============================================ MMA warp: the five products of every pair
     const uint32_t issue = elect_one() ? 1u : 0u;
     const uint64_t d_k = smem_desc_sw128(sbase + L::kK, 16, 1024);
     const uint64_t d_v = smem_desc_sw128(sbase + L::kV, 16, 1024);
-    const uint64_t d_do = smem_desc_sw128(sbase + L::kDO, 16, 1024);
-    const uint64_t d_p_mn = smem_desc_sw128(sbase + L::kP, L::kPanel, 1024);     // [q][k] read with M = k
-    const uint64_t d_ds_mn = smem_desc_sw128(sbase + L::kDS, L::kPanel, 1024);
-    const uint64_t d_ds_k = smem_desc_sw128(sbase + L::kDS, 16, 1024);           // same bytes, M = q
-    const uint64_t d_do_mn = smem_desc_sw128(sbase + L::kDO, L::kPanel, 1024);   // [q][d] read with K = q
+    const uint64_t d_dst_mn = smem_desc_sw128(sbase + L::kDS, L::kPanel, 1024);  // [k][q] read with M = q
     const uint64_t d_k_mn = smem_desc_sw128(sbase + L::kK, L::kPanel, 1024);     // [k][d] read with K = k
-    auto issue_s = [&](int itx) {      // S = Q K^T of pair itx (its Q buffer must have landed)
+    auto issue_s = [&](int itx) {      // S^T = K Q^T of pair itx (its Q buffer must have landed)
       const uint64_t dq_x = smem_desc_sw128(sbase + ((itx & 1) ? L::kQ1 : L::kQ), 16, 1024);
 #pragma unroll
       for (int ks = 0; ks < DP / 16; ++ks) {
         const uint64_t off = (uint64_t)(((ks / 4) * L::kPanel + (ks % 4) * 32) >> 4);
-        mma_ss(tS, dq_x + off, d_k + off, kIdSS, ks > 0, issue);
+        mma_ss(tS, d_k + off, dq_x + off, kIdSS, ks > 0, issue);
       }
     };
     for (int it = 0; it < n_iter; ++it) {
       int i, hq;
       pair_of(it, i, hq);
       const uint32_t q_off = (it & 1) ? L::kQ1 : L::kQ;
-      const uint64_t d_q_mn = smem_desc_sw128(sbase + q_off, L::kPanel, 1024);
+      const uint32_t do_off = (it & 1) ? L::kDO1 : L::kDO;
+      const uint64_t d_q_mn = smem_desc_sw128(sbase + q_off, L::kPanel, 1024);     // [q][d] read with K = q
+      const uint64_t d_do = smem_desc_sw128(sbase + do_off, 16, 1024);
+      const uint64_t d_do_mn = smem_desc_sw128(sbase + do_off, L::kPanel, 1024);   // [q][d] read with K = q
       // Operand rows past the sequence end belong to the next packed sequence (or to nobody).
       // P and dS are exact zeros there, but 0 * Inf/NaN would still poison the sums they are
-      // contracted over (K rows feed dQ; Q and dO rows feed dK and dV), so those rows are
-      // cleared, like the reference's zero-padded loads (flash_attn_triton.py:155-165).
+      // contracted over (K rows feed dQ, V rows dP; Q and dO rows feed dK and dV), so those
+      // rows are cleared, like the reference's zero-padded loads (flash_attn_triton.py:155-165).
       const bool q_ragged = (i + 1) * kT > len;
       if (it == 0) {
         mbar_wait(bar_kv, 0, abort_flag);
         mbar_wait(bar_q0, 0, abort_flag);
-        if (kv0 + kT > len) zero_tile_rows(sgen + L::kK, kPanels, L::kPanel, len - kv0, kT, lane);
+        if (kv0 + kT > len) {
+          zero_tile_rows(sgen + L::kK, kPanels, L::kPanel, len - kv0, kT, lane);
+          zero_tile_rows(sgen + L::kV, kPanels, L::kPanel, len - kv0, kT, lane);
+        }
         if (q_ragged) zero_tile_rows(sgen + L::kQ, kPanels, L::kPanel, max(len - i * kT, 0), kT, lane);
         tc_fence_after();
         issue_s(0);
+        mma_commit(bar_s, issue);
       }
-      // (S of later pairs is issued at the end of the pair before, behind its dQ product)
-      mbar_wait(bar_do, it & 1, abort_flag);
-      if (q_ragged) zero_tile_rows(sgen + L::kDO, kPanels, L::kPanel, max(len - i * kT, 0), kT, lane);
+      // (S^T of later pairs is issued at the end of the pair before, behind its dQ product)
+      mbar_wait(bar_do0 + 8 * (it & 1), (it >> 1) & 1, abort_flag);
+      if (q_ragged) zero_tile_rows(sgen + do_off, kPanels, L::kPanel, max(len - i * kT, 0), kT, lane);
       tc_fence_after();
-      // dP = dO V^T
+      // dP^T = V dO^T (its columns held the previous pair's dQ, read out before bar_free)
 #pragma unroll
       for (int ks = 0; ks < DP / 16; ++ks) {
         const uint64_t off = (uint64_t)(((ks / 4) * L::kPanel + (ks % 4) * 32) >> 4);
-        mma_ss(tDP, d_do + off, d_v + off, kIdSS, ks > 0, issue);
+        mma_ss(tDP, d_v + off, d_do + off, kIdSS, ks > 0, issue);
       }
-      mma_commit(bar_sdp, issue);
-      // the first half of the previous pair's dQ tile must have left the P bytes before
-      // they are rewritten (the second half sits in a Q buffer and may still be on its way);
-      // told to the compute warps separately, so that they wait for it only when they are
-      // about to store, after their exponentials
-      if (issue) { bulk_wait_read_but_one(); mbar_arrive(bar_pfree); }
-      __syncwarp();
-      // wait for P and dS in shared memory
+      mma_commit(bar_dp, issue);
+      // wait for P^T and dS^T in tensor memory, dS^T in shared memory
       mbar_wait(bar_pds, it & 1, abort_flag);
       tc_fence_after();
       const uint32_t acc = it > 0 ? 1u : 0u;
 #pragma unroll
-      for (int ks = 0; ks < kT / 16; ++ks) {   // contraction over the 128 queries
+      for (int ks = 0; ks < kT / 16; ++ks) {   // dV += P^T dO, contraction over the 128 queries
         const uint64_t off = (uint64_t)((ks * 2048) >> 4);
-        mma_ss(tDV, d_p_mn + off, d_do_mn + off, kIdTT, ks > 0 ? 1u : acc, issue);
+        mma_ts(tDV, tS + a_cols(ks), d_do_mn + off, kIdTS, ks > 0 ? 1u : acc, issue);
       }
-      mma_commit(bar_dv, issue);
-      // (issued first and alone: the loader refetches dO the moment this product has read it, and
-      // that fetch is the longest wait of a pair)
-      // The Q buffer of pair it - 1 held the second half of its dQ tile; once that is
-      // read it takes the query tile of pair it + 1 (in L2 by now).  Behind the dV issue: waiting
-      // for the copy engine here must not delay the product that frees dO.
-      if (it > 0 && it + 1 < n_iter) {
-        int in, hqn;
-        pair_of(it + 1, in, hqn);
-        if (issue) {
-          bulk_wait_read_all();
-          const uint32_t dst = sbase + (((it + 1) & 1) ? L::kQ1 : L::kQ), bar = bar_q0 + 8 * ((it + 1) & 1);
-          mbar_expect_tx(bar, L::kOperand);
-          for (int pn = 0; pn < kPanels; ++pn)
-            tma_load_4d(dst + pn * L::kPanel, &tmap_q, bar, 64 * pn, seq_start + in * kT, hqn, bcoord);
-        }
-        __syncwarp();
+      mma_commit(bar_dv0 + 8 * (it & 1), issue);      // the loader may refill this dO buffer
+#pragma unroll
+      for (int ks = 0; ks < kT / 16; ++ks) {   // dK += dS^T Q
+        const uint64_t off = (uint64_t)((ks * 2048) >> 4);
+        mma_ts(tDK, tDP + a_cols(ks), d_q_mn + off, kIdTS, ks > 0 ? 1u : acc, issue);
       }
 #pragma unroll
-      for (int ks = 0; ks < kT / 16; ++ks) {
+      for (int ks = 0; ks < kT / 16; ++ks) {   // dQ = dS K, contraction over the 128 keys; takes the dP^T columns
         const uint64_t off = (uint64_t)((ks * 2048) >> 4);
-        mma_ss(tDK, d_ds_mn + off, d_q_mn + off, kIdTT, ks > 0 ? 1u : acc, issue);
-      }
-#pragma unroll
-      for (int ks = 0; ks < kT / 16; ++ks) {   // contraction over the 128 keys
-        const uint64_t offa = (uint64_t)(((ks / 4) * L::kPanel + (ks % 4) * 32) >> 4);
-        const uint64_t offb = (uint64_t)((ks * 2048) >> 4);
-        mma_ss(tDP, d_ds_k + offa, d_k_mn + offb, kIdDQ, ks > 0, issue);   // dQ takes the dP columns
+        mma_ss(tDP, d_dst_mn + off, d_k_mn + off, kIdDQ, ks > 0, issue);
       }
       mma_commit(bar_dq, issue);
-      // the S columns were read before P and dS were written: start the next pair's scores
-      // now, so they are computed while this pair's dQ tile is being moved out
+      // start the next pair's scores now (they overwrite P^T, which dV has read: products
+      // run in issue order), so they are computed while this pair's dQ tile is being moved out
       if (it + 1 < n_iter) {
         mbar_wait(bar_q0 + 8 * ((it + 1) & 1), ((it + 1) >> 1) & 1, abort_flag);
         int in, hqn;
@@ -328,52 +352,36 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
           zero_tile_rows(sgen + (((it + 1) & 1) ? L::kQ1 : L::kQ), kPanels, L::kPanel, max(len - in * kT, 0), kT, lane);
         tc_fence_after();
         issue_s(it + 1);
+        mma_commit(bar_s, issue);
       }
-      // the compute warps have moved the scaled dQ tile into shared memory (first half of
-      // the columns in the P tile, second half in this pair's Q buffer): add both to the
-      // fp32 accumulator in global memory, one bulk group each.  Rows past the sequence
-      // end hold exact zeros.
+      // the next pair's dP^T takes the columns of this pair's dQ: the compute warps must have
+      // moved it out
       mbar_wait(bar_free, it & 1, abort_flag);
-      if (issue) {
-        const int tl0 = (p.cu_seqlens ? seq_start : b * p.seqlen) + i * kT;
-        for (int pn = 0; pn < DP / 64; ++pn)
-          tma_reduce_add_3d(&tmap_dq, sbase + L::kP + pn * L::kStagePanel, 32 * pn, tl0, hq);
-        bulk_commit_group();
-        for (int pn = 0; pn < DP / 64; ++pn)
-          tma_reduce_add_3d(&tmap_dq, sbase + q_off + pn * L::kStagePanel, 32 * (DP / 64 + pn), tl0, hq);
-        bulk_commit_group();
-      }
-      __syncwarp();
     }
-#ifdef B200ATTN_BWD_READ_WAIT
-    if (issue) bulk_wait_read_all();
-#else
-    if (issue) bulk_wait_all();
-#endif
-    __syncwarp();
   } else if (warp < kBwdComputeWarps) {
-    // ============================================ compute warps: two threads per row
-    // Two threads per row: warps w and w + 4 share TMEM lanes 32 (w % 4) .., each takes half
-    // of the columns, so every scheduler has two warps to switch between.
-    const int row = threadIdx.x & (kT - 1);              // query row in the tile / key row in the epilogue
+    // ============================================ compute warps: two threads per key row
+    // Warps w and w + 4 share TMEM lanes 32 (w % 4) .. (one key row per lane); each takes half
+    // of the columns (64 queries), so every scheduler has two warps to switch between.
+    const int row = threadIdx.x & (kT - 1);              // key row in the tile (query row when dQ is moved out)
     const int half = threadIdx.x >> 7;                   // which half of the columns
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-    uint8_t* sP = sgen + L::kP;
     uint8_t* sDS = sgen + L::kDS;
-    // lse and D of a pair's rows are fetched a pair ahead (global loads take thousands of cycles
-    // while the reduce-adds keep the L2 busy)
-    float lse2_nx = 0.f, dsum_nx = 0.f;
-    bool live_nx = false;
+    float2* stats = reinterpret_cast<float2*>(sgen + L::kStats);   // (lse2, D) per query row of the pair
+    const int kj = kv0 + row;
+    // lse and D of a pair's query rows are fetched a pair ahead by the threads of the first half
+    // (global loads take thousands of cycles while the reduce-adds keep the L2 busy) and passed
+    // through shared memory: every thread needs them for all of its 64 columns.  A query row past
+    // the sequence end, or one without a visible key (lse = -inf), gets lse2 = +inf: P = 0 there.
+    float lse2_nx = INFINITY, dsum_nx = 0.f;
     auto fetch_row_stats = [&](int itx) {
-      lse2_nx = 0.f; dsum_nx = 0.f; live_nx = false;
-      if (itx >= n_iter) return;
+      lse2_nx = INFINITY; dsum_nx = 0.f;
+      if (half != 0 || itx >= n_iter) return;
       const int gx = itx % p.group, ix = i_first + itx / p.group;
       const int hqx = hk * p.group + gx, qix = ix * kT + row;
       if (qix < len) {
         const long long tokx = (long long)seq_start + qix;
         const float l = p.lse[(p.cu_seqlens ? 0 : (long long)b * p.lse_sb) + tokx * p.lse_st + (long long)hqx * p.lse_sh];
-        lse2_nx = p.lse_base2 ? l : l * 1.4426950408889634f;
-        live_nx = l != -INFINITY;
+        if (l != -INFINITY) lse2_nx = p.lse_base2 ? l : l * 1.4426950408889634f;
         const long long tl = p.cu_seqlens ? tokx : (long long)b * p.seqlen + qix;
         dsum_nx = p.dvec[tl * p.heads_q + hqx];
       }
@@ -381,47 +389,75 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     fetch_row_stats(0);
     for (int it = 0; it < n_iter; ++it) {
       const int i = i_first + it / p.group;
-      const int qi = i * kT + row;
-      const float lse2 = lse2_nx, dsum = dsum_nx;
-      const bool live = live_nx;
-      mbar_wait(bar_sdp, it & 1, abort_flag);
+      // every thread is past its reads of the previous pair's statistics (it waited for that
+      // pair's dQ, which is issued only after all of them handed P^T and dS^T over)
+      if (half == 0) stats[row] = make_float2(lse2_nx, dsum_nx);
+      asm volatile("bar.sync 1, %0;" ::"n"(kBwdComputeThreads) : "memory");
+      // Column x of this row (query i * 128 + x) is visible iff x >= xmin: the causal diagonal
+      // when this is the diagonal tile, nothing at all for a key row past the sequence end.
+      int xmin = p.causal ? kj - i * kT : 0;
+      if (kj >= len) xmin = 1 << 20;
+      const bool masked = (p.causal && kv0 + kT - 1 > i * kT) || (kv0 + kT > len);   // (same for the whole CTA)
+      // P^T from S^T alone: the exponentials run while dP^T, which had to wait for the previous
+      // pair's dQ to leave its columns, is still being computed
+      mbar_wait(bar_s, it & 1, abort_flag);
       tc_fence_after();
-      // visible keys of this row inside the tile: columns [0, lim)
-      int lim = live ? min(kT, len - kv0) : 0;
-      if (p.causal) lim = min(lim, qi - kv0 + 1);
-      const bool masked = __any_sync(0xffffffffu, lim < kT);   // only diagonal and ragged tiles
+      float pf[kT / 2];
 #pragma unroll
       for (int c2 = 0; c2 < kT / 64; ++c2) {
-        const int cc = 2 * half + c2;                    // 32-column group
-        uint32_t sr[32], dr[32];
+        const int cc = 2 * half + c2;                    // 32-column group: queries [32 cc, 32 cc + 32)
+        uint32_t sr[32];
         tmem_ld32(tS + lane_off + 32 * cc, sr);
-        tmem_ld32(tDP + lane_off + 32 * cc, dr);
         tmem_wait_ld();
-        uint32_t pp[16], dd[16];
+        uint32_t pp[16];
+        const float4* st4 = reinterpret_cast<const float4*>(stats + 32 * cc);
 #pragma unroll
         for (int x = 0; x < 32; x += 2) {
-          float p0 = ex2f(fmaf(__uint_as_float(sr[x]), p.scale_log2, -lse2));
-          float p1 = ex2f(fmaf(__uint_as_float(sr[x + 1]), p.scale_log2, -lse2));
-          float d0 = p0 * (__uint_as_float(dr[x]) - dsum);
-          float d1 = p1 * (__uint_as_float(dr[x + 1]) - dsum);
+          const float4 st = st4[x / 2];                  // (lse2, D) of queries x and x + 1
+          float p0 = ex2f(fmaf(__uint_as_float(sr[x]), p.scale_log2, -st.x));
+          float p1 = ex2f(fmaf(__uint_as_float(sr[x + 1]), p.scale_log2, -st.z));
           if (masked) {
-            // masked entries are exact zeros whatever S and dP hold there
-            if (32 * cc + x >= lim) { p0 = 0.f; d0 = 0.f; }
-            if (32 * cc + x + 1 >= lim) { p1 = 0.f; d1 = 0.f; }
+            // masked entries are exact zeros whatever S holds there
+            if (32 * cc + x < xmin) p0 = 0.f;
+            if (32 * cc + x + 1 < xmin) p1 = 0.f;
           }
+          pf[32 * c2 + x] = p0;
+          pf[32 * c2 + x + 1] = p1;
           pp[x / 2] = pack2<T>(p0, p1);
+        }
+        // P^T back into tensor memory, over columns of S^T this thread has read
+        tmem_st16(tS + lane_off + 64 * half + 16 * c2, pp);
+      }
+      // dS^T = P^T o (dP^T - D)
+      mbar_wait(bar_dp, it & 1, abort_flag);
+      tc_fence_after();
+#pragma unroll
+      for (int c2 = 0; c2 < kT / 64; ++c2) {
+        const int cc = 2 * half + c2;
+        uint32_t dr[32];
+        tmem_ld32(tDP + lane_off + 32 * cc, dr);
+        tmem_wait_ld();
+        uint32_t dd[16];
+        const float4* st4 = reinterpret_cast<const float4*>(stats + 32 * cc);
+#pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+          const float4 st = st4[x / 2];
+          // (P = 0 where masked; dP is finite there: rows past the sequence end are cleared)
+          const float d0 = pf[32 * c2 + x] * (__uint_as_float(dr[x]) - st.y);
+          const float d1 = pf[32 * c2 + x + 1] * (__uint_as_float(dr[x + 1]) - st.w);
           dd[x / 2] = pack2<T>(d0, d1);
         }
-        // row `row` of a [128 q][128 k] tile, two 64-column panels, 128-byte swizzle
-        if (c2 == 0) mbar_wait(bar_pfree, it & 1, abort_flag);      // the P tile is no longer being read out
+        tmem_st16(tDP + lane_off + 64 * half + 16 * c2, dd);
+        // dS^T also as row `row` of a [128 k][128 q] tile, two 64-column panels, 128-byte swizzle
+        if (c2 == 0) mbar_wait(bar_pfree, it & 1, abort_flag);      // the tile is no longer being read out
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-          const int chunk = 4 * cc + ch;                       // 16-byte chunk of the 256-byte row
-          const uint32_t off = (chunk >> 3) * L::kPanel + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
+          const int chunk = 4 * c2 + ch;                       // 16-byte chunk of this half's 128-byte panel row
+          const uint32_t off = half * L::kPanel + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
           *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[4 * ch], dd[4 * ch + 1], dd[4 * ch + 2], dd[4 * ch + 3]);
         }
       }
+      tmem_wait_st();
       fence_proxy_async();       // generic-proxy writes -> visible to the tensor core's reads
       tc_fence_before();
       mbar_arrive(bar_pds);
@@ -431,7 +467,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       tc_fence_after();
       // scaled fp32 tile -> shared memory in the copy engine's 128-byte-swizzled layout
       // (one panel per 32 columns); the control warp adds it to global memory
-      uint8_t* sStage = sgen + (half == 0 ? L::kP : ((it & 1) ? L::kQ1 : L::kQ));
+      uint8_t* sStage = sgen + (half == 0 ? L::kDS : ((it & 1) ? L::kQ1 : L::kQ));
 #pragma unroll
       for (int c2 = 0; c2 < DP / 64; ++c2) {
         const int cc = (DP / 64) * half + c2;
@@ -453,7 +489,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     // ---- dK, dV of this key tile (every product has completed: the last bar_dq was waited)
     // (tcgen05.ld is warp-collective: every thread runs the loads, only the
     // stores depend on the row being a real key)
-    const int kj = kv0 + row;
     const bool key_ok = kj < len;
     const long long ktok = (long long)seq_start + (key_ok ? kj : 0);
     T* dkrow = (T*)p.dk + (p.cu_seqlens ? 0 : (long long)b * p.dk_sb) + ktok * p.dk_st + (long long)hk * p.dk_sh;
