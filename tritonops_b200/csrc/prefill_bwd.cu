@@ -103,7 +103,7 @@ struct BwdSmem {
   static_assert((DP / 64) * kStagePanel <= kPds && (DP / 64) * kStagePanel <= kOperand, "dQ staging fits");
   static constexpr int kStats = kDS + kPds;          // (lse2, D) of the pair's 128 query rows
   static constexpr int kBarOffset = kStats + kT * 8;
-  static constexpr int kNumBars = 13;
+  static constexpr int kNumBars = 14;
   static constexpr int kBytes = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kAlloc = kBytes + 1024;
   static_assert(kAlloc <= 232448, "shared memory of one CTA");
@@ -143,7 +143,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
   const uint32_t bars = sbase + L::kBarOffset;
   const uint32_t bar_kv = bars, bar_q0 = bars + 8 /* +16: second buffer */, bar_do0 = bars + 24 /* +32 */,
                  bar_s = bars + 40, bar_dp = bars + 48, bar_pds = bars + 56, bar_dv0 = bars + 64 /* +72 */,
-                 bar_dq = bars + 80, bar_free = bars + 88, bar_pfree = bars + 96;
+                 bar_dq = bars + 80, bar_free = bars + 88, bar_pfree = bars + 96, bar_p = bars + 104;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kBarOffset + L::kNumBars * 8 + 4);
 
@@ -161,6 +161,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     mbar_init(bar_dp, 1);
     mbar_init(bar_pfree, 1);
     mbar_init(bar_pds, kBwdComputeThreads);
+    mbar_init(bar_p, kBwdComputeThreads);
     mbar_init(bar_dq, 1);
     mbar_init(bar_free, kBwdComputeThreads);
     fence_barrier_init();
@@ -321,8 +322,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         mma_ss(tDP, d_v + off, d_do + off, kIdSS, ks > 0, issue);
       }
       mma_commit(bar_dp, issue);
-      // wait for P^T and dS^T in tensor memory, dS^T in shared memory
-      mbar_wait(bar_pds, it & 1, abort_flag);
+      // P^T is in tensor memory: dV runs while the compute warps form dS^T
+      mbar_wait(bar_p, it & 1, abort_flag);
       tc_fence_after();
       const uint32_t acc = it > 0 ? 1u : 0u;
 #pragma unroll
@@ -331,6 +332,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         mma_ts(tDV, tS + a_cols(ks), d_do_mn + off, kIdTS, ks > 0 ? 1u : acc, issue);
       }
       mma_commit(bar_dv0 + 8 * (it & 1), issue);      // the loader may refill this dO buffer
+      // dS^T in tensor memory and in shared memory
+      mbar_wait(bar_pds, it & 1, abort_flag);
+      tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < kT / 16; ++ks) {   // dK += dS^T Q
         const uint64_t off = (uint64_t)((ks * 2048) >> 4);
@@ -428,6 +432,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         // P^T back into tensor memory, over columns of S^T this thread has read
         tmem_st16(tS + lane_off + 64 * half + 16 * c2, pp);
       }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p);
       // dS^T = P^T o (dP^T - D)
       mbar_wait(bar_dp, it & 1, abort_flag);
       tc_fence_after();
