@@ -45,7 +45,7 @@ LOG2E = 1.4426950408889634
 TRAFFIC = {
     "cfg2": (409.738496e6 + 119.315968e6, "profiles/prefill_cfg2_ncu.md"),
     "cfg3": (1.301250e9 + 6.312448e6, "profiles/decode_cfg3_ncu.md"),
-    "cfg2_backward": (809.637120e6 + 491.812352e6, "profiles/backward_cfg2_ncu.md"),
+    "cfg2_backward": (824.896512e6 + 490.286848e6, "profiles/backward_cfg2_ncu.md"),
     "cfg4": (614.754816e6 + 124.699136e6, "profiles/sparse_prefill_cfg4_ncu.md"),
     "cfg5": (4 * (537.079552e6 + 4.031488e6), "profiles/sparse_decode_cfg5_ncu.md (batch 8 capture x 4)"),
     "paged_cfg3": (1.301388e9 + 6.204160e6, "profiles/paged_decode_cfg3_ncu.md"),

@@ -370,7 +370,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     const int half = threadIdx.x >> 7;                   // which half of the columns
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     uint8_t* sDS = sgen + L::kDS;
-    float2* stats = reinterpret_cast<float2*>(sgen + L::kStats);   // (lse2, D) per query row of the pair
+    float* s_lse = reinterpret_cast<float*>(sgen + L::kStats);     // lse2 and D of the pair's query rows
+    float* s_dsum = s_lse + kT;
     const int kj = kv0 + row;
     // lse and D of a pair's query rows are fetched a pair ahead by the threads of the first half
     // (global loads take thousands of cycles while the reduce-adds keep the L2 busy) and passed
@@ -395,7 +396,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       const int i = i_first + it / p.group;
       // every thread is past its reads of the previous pair's statistics (it waited for that
       // pair's dQ, which is issued only after all of them handed P^T and dS^T over)
-      if (half == 0) stats[row] = make_float2(lse2_nx, dsum_nx);
+      if (half == 0) { s_lse[row] = lse2_nx; s_dsum[row] = dsum_nx; }
       asm volatile("bar.sync 1, %0;" ::"n"(kBwdComputeThreads) : "memory");
       // Column x of this row (query i * 128 + x) is visible iff x >= xmin: the causal diagonal
       // when this is the diagonal tile, nothing at all for a key row past the sequence end.
@@ -414,12 +415,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         tmem_ld32(tS + lane_off + 32 * cc, sr);
         tmem_wait_ld();
         uint32_t pp[16];
-        const float4* st4 = reinterpret_cast<const float4*>(stats + 32 * cc);
+        const float4* l4 = reinterpret_cast<const float4*>(s_lse + 32 * cc);
+        float4 st = make_float4(0.f, 0.f, 0.f, 0.f);     // lse2 of queries x .. x + 3
 #pragma unroll
         for (int x = 0; x < 32; x += 2) {
-          const float4 st = st4[x / 2];                  // (lse2, D) of queries x and x + 1
-          float p0 = ex2f(fmaf(__uint_as_float(sr[x]), p.scale_log2, -st.x));
-          float p1 = ex2f(fmaf(__uint_as_float(sr[x + 1]), p.scale_log2, -st.z));
+          if ((x & 2) == 0) st = l4[x / 4];
+          const float l0 = (x & 2) ? st.z : st.x, l1 = (x & 2) ? st.w : st.y;
+          float p0 = ex2f(fmaf(__uint_as_float(sr[x]), p.scale_log2, -l0));
+          float p1 = ex2f(fmaf(__uint_as_float(sr[x + 1]), p.scale_log2, -l1));
           if (masked) {
             // masked entries are exact zeros whatever S holds there
             if (32 * cc + x < xmin) p0 = 0.f;
@@ -445,13 +448,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         tmem_ld32(tDP + lane_off + 32 * cc, dr);
         tmem_wait_ld();
         uint32_t dd[16];
-        const float4* st4 = reinterpret_cast<const float4*>(stats + 32 * cc);
+        const float4* d4 = reinterpret_cast<const float4*>(s_dsum + 32 * cc);
+        float4 st = make_float4(0.f, 0.f, 0.f, 0.f);     // D of queries x .. x + 3
 #pragma unroll
         for (int x = 0; x < 32; x += 2) {
-          const float4 st = st4[x / 2];
+          if ((x & 2) == 0) st = d4[x / 4];
           // (P = 0 where masked; dP is finite there: rows past the sequence end are cleared)
-          const float d0 = pf[32 * c2 + x] * (__uint_as_float(dr[x]) - st.y);
-          const float d1 = pf[32 * c2 + x + 1] * (__uint_as_float(dr[x + 1]) - st.w);
+          const float d0 = pf[32 * c2 + x] * (__uint_as_float(dr[x]) - ((x & 2) ? st.z : st.x));
+          const float d1 = pf[32 * c2 + x + 1] * (__uint_as_float(dr[x + 1]) - ((x & 2) ? st.w : st.y));
           dd[x / 2] = pack2<T>(d0, d1);
         }
         tmem_st16(tDP + lane_off + 64 * half + 16 * c2, dd);
