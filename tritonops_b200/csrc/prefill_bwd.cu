@@ -113,7 +113,8 @@ template <typename T, int DP>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
            const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-           const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
+           const __grid_constant__ CUtensorMap tmap_dq, const __grid_constant__ CUtensorMap tmap_dk,
+           const __grid_constant__ CUtensorMap tmap_dv, const BwdParams p) {
   using L = BwdSmem<DP>;
   constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   constexpr uint32_t kIdSS = idesc_f16(kFmt, false, kT, kT);           // S^T, dP^T: A, B K-major
@@ -497,10 +498,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       tc_fence_before();
       mbar_arrive(bar_free);
     }
-    // ---- dK, dV of this key tile (every product has completed: the last bar_dq was waited)
-    // (tcgen05.ld is warp-collective: every thread runs the loads, only the
-    // stores depend on the row being a real key)
+    // ---- dK, dV of this key tile (every product has completed: the last bar_dq was waited).
+    // A whole tile goes out as 16-bit through the dead K and V buffers (same swizzled layout as
+    // the operands) and two copy-engine stores: written row by row from the threads, 16 bytes per
+    // lane at a stride of a token, the 64 KB took ~8000 cycles per CTA.  A tile that the sequence
+    // end cuts keeps the per-thread stores, which can leave the next sequence's rows alone.
+    // (tcgen05.ld is warp-collective: every thread runs the loads, only the stores depend on
+    // the row being a real key)
     const bool key_ok = kj < len;
+    const bool whole = kv0 + kT <= len;
     const long long ktok = (long long)seq_start + (key_ok ? kj : 0);
     T* dkrow = (T*)p.dk + (p.cu_seqlens ? 0 : (long long)b * p.dk_sb) + ktok * p.dk_st + (long long)hk * p.dk_sh;
     T* dvrow = (T*)p.dv + (p.cu_seqlens ? 0 : (long long)b * p.dv_sb) + ktok * p.dv_st + (long long)hk * p.dv_sh;
@@ -508,23 +514,39 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     for (int which = 0; which < 2; ++which) {
       const float sc = which ? 1.f : p.scale;
       T* dst = which ? dvrow : dkrow;
+      uint8_t* sOut = sgen + (which ? L::kV : L::kK);
 #pragma unroll
       for (int c2 = 0; c2 < DP / 64; ++c2) {
         const int cc = (DP / 64) * half + c2;
         uint32_t r[32];
         tmem_ld32((which ? tDV : tDK) + lane_off + 32 * cc, r);
         tmem_wait_ld();
-        if (key_ok && 32 * cc < p.head_dim) {
 #pragma unroll
-          for (int x = 0; x < 32; x += 8) {
-            uint4 pk;
-            pk.x = pack2<T>(__uint_as_float(r[x]) * sc, __uint_as_float(r[x + 1]) * sc);
-            pk.y = pack2<T>(__uint_as_float(r[x + 2]) * sc, __uint_as_float(r[x + 3]) * sc);
-            pk.z = pack2<T>(__uint_as_float(r[x + 4]) * sc, __uint_as_float(r[x + 5]) * sc);
-            pk.w = pack2<T>(__uint_as_float(r[x + 6]) * sc, __uint_as_float(r[x + 7]) * sc);
+        for (int x = 0; x < 32; x += 8) {
+          uint4 pk;
+          pk.x = pack2<T>(__uint_as_float(r[x]) * sc, __uint_as_float(r[x + 1]) * sc);
+          pk.y = pack2<T>(__uint_as_float(r[x + 2]) * sc, __uint_as_float(r[x + 3]) * sc);
+          pk.z = pack2<T>(__uint_as_float(r[x + 4]) * sc, __uint_as_float(r[x + 5]) * sc);
+          pk.w = pack2<T>(__uint_as_float(r[x + 6]) * sc, __uint_as_float(r[x + 7]) * sc);
+          if (whole) {
+            const int col = 32 * cc + x;                 // 16-byte chunk (col % 64) / 8 of panel col / 64
+            *reinterpret_cast<uint4*>(sOut + (col >> 6) * L::kPanel + row * 128 + (((((col & 63) >> 3)) ^ (row & 7)) << 4)) = pk;
+          } else if (key_ok && 32 * cc < p.head_dim) {
             *reinterpret_cast<uint4*>(dst + 32 * cc + x) = pk;
           }
         }
+      }
+    }
+    if (whole) {
+      fence_proxy_async();
+      asm volatile("bar.sync 1, %0;" ::"n"(kBwdComputeThreads) : "memory");
+      if (threadIdx.x == 0) {
+        for (int pn = 0; pn < kPanels; ++pn) {
+          tma_store_4d(&tmap_dk, sbase + L::kK + pn * L::kPanel, 64 * pn, seq_start + kv0, hk, bcoord);
+          tma_store_4d(&tmap_dv, sbase + L::kV + pn * L::kPanel, 64 * pn, seq_start + kv0, hk, bcoord);
+        }
+        bulk_commit_group();
+        bulk_wait_read_all();
       }
     }
   }
@@ -679,11 +701,13 @@ int launch_bwd(const b200attn_prefill_bwd_args* a, const BwdParams& p, cudaStrea
   using L = BwdSmem<DP>;
   const long long tokens = a->cu_seqlens ? a->total_tokens : a->seqlen;
   const int tb = a->cu_seqlens ? 1 : a->batch;
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdk, tdv;
   if (!make_tmap(&tq, a->dtype, a->q, a->head_dim, tokens, a->heads_q, tb, a->q_stride_t, a->q_stride_h, a->q_stride_b) ||
       !make_tmap(&tk, a->dtype, a->k, a->head_dim, tokens, a->heads_kv, tb, a->k_stride_t, a->k_stride_h, a->k_stride_b) ||
       !make_tmap(&tv, a->dtype, a->v, a->head_dim, tokens, a->heads_kv, tb, a->v_stride_t, a->v_stride_h, a->v_stride_b) ||
-      !make_tmap(&tdo, a->dtype, a->d_o, a->head_dim, tokens, a->heads_q, tb, a->do_stride_t, a->do_stride_h, a->do_stride_b))
+      !make_tmap(&tdo, a->dtype, a->d_o, a->head_dim, tokens, a->heads_q, tb, a->do_stride_t, a->do_stride_h, a->do_stride_b) ||
+      !make_tmap(&tdk, a->dtype, a->dk, a->head_dim, tokens, a->heads_kv, tb, a->dk_stride_t, a->dk_stride_h, a->dk_stride_b) ||
+      !make_tmap(&tdv, a->dtype, a->dv, a->head_dim, tokens, a->heads_kv, tb, a->dv_stride_t, a->dv_stride_h, a->dv_stride_b))
     return B200ATTN_ERR_CUDA;
   auto kern = bwd_kernel<T, DP>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
@@ -704,7 +728,7 @@ int launch_bwd(const b200attn_prefill_bwd_args* a, const BwdParams& p, cudaStrea
   const long long n_ctas = (long long)p.n_kvtiles * a->heads_kv * a->batch;
   if (n_ctas > 0x7fffffffLL) return B200ATTN_ERR_TOO_LARGE;
   dim3 grid((unsigned)n_ctas);
-  kern<<<grid, kBwdThreads, L::kAlloc, stream>>>(tq, tk, tv, tdo, tdq, p);
+  kern<<<grid, kBwdThreads, L::kAlloc, stream>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
   // 3. dq accumulator -> dq
   {
     const long long items = rows * (DP / 8);
