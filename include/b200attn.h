@@ -114,6 +114,17 @@ typedef struct {
  * (flash_attn_triton/flash_attn_triton.py:595-658) and its kernel (:52-180). */
 int b200attn_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream);
 
+/* The same forward restricted to the query rows [row_begin, row_end) of every sequence: only
+ * those rows of o and lse are written.  row_begin is a multiple of 256; row_end is a multiple of
+ * 256 or reaches the end of the longest sequence (B200ATTN_ERR_SHAPE otherwise).  With causal = 1
+ * the call reads no K / V row at or beyond row_end, so a caller whose sequence is still arriving
+ * (from the host, from a peer) can attend to the rows that have landed while the next ones are on
+ * their way; rows computed this way are bit-identical to those of the full call.  The reference
+ * has no counterpart: its launcher (flash_attn_triton/flash_attn_triton.py:595-658) always covers
+ * whole sequences.  tritonops_b200/host.py streams host buffers through it. */
+int b200attn_prefill_fwd_rows(const b200attn_prefill_args* args, int32_t row_begin, int32_t row_end,
+                              b200attn_stream_t stream);
+
 /* Window-sparse (local + global) or block-list sparse forward.  Replaces the
  * launcher body at flash_attn_triton/flash_attn_sparse_attn_triton.py:237-326
  * and its kernel (:47-234), with the mask of the torch function at :422-433. */

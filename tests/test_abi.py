@@ -137,6 +137,13 @@ def test_prefill_validation_codes(lib):
     a.v_stride_t, a.softmax_scale = 256, 0.0
     assert lib.b200attn_prefill_fwd(C.byref(a), None) == -7            # scale must be positive
     a.softmax_scale = 0.1
+    # row ranges: start on a multiple of 256, end on one unless they reach the end of the sequence
+    a.seqlen = 1024
+    assert lib.b200attn_prefill_fwd_rows(C.byref(a), 100, 512, None) == -7
+    assert lib.b200attn_prefill_fwd_rows(C.byref(a), 256, 300, None) == -7
+    assert lib.b200attn_prefill_fwd_rows(C.byref(a), 512, 512, None) == -7
+    assert lib.b200attn_prefill_fwd_rows(C.byref(a), 2048, 4096, None) == 0    # past the end: nothing to do
+    a.seqlen = 256
     a.sparsity = 2                                                      # block list without lists
     assert lib.b200attn_sparse_prefill_fwd(C.byref(a), None) == -1
     a.block_idx = a.block_cnt = 0x1000

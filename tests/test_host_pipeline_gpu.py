@@ -67,3 +67,31 @@ def test_host_pipeline_growing_lengths_over_several_calls():
         cu_dev = torch.tensor(cu, dtype=torch.int32, device="cuda")
         o, lse = ops.prefill(hq.cuda(), hk.cuda(), hv.cuda(), cu_seqlens=cu_dev, max_seqlen=max(lens), scale=D ** -0.5)
         assert torch.equal(ho, o.cpu()) and torch.equal(hl, lse.cpu())
+
+
+def test_host_pipeline_small_chunks_and_non_causal():
+    """256-row chunks (the smallest the row-range call takes) and the non-causal path, which
+    cannot be chunked, against the packed call."""
+    from tritonops_b200 import ops
+    from tritonops_b200.host import HostPrefill
+    lens = [700, 256, 1030]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T, Hq, Hkv, D = cu[-1], 4, 4, 64
+    g = torch.Generator().manual_seed(9)
+    hq = torch.randn(1, T, Hq, D, generator=g).to(torch.bfloat16).pin_memory()
+    hk = torch.randn(1, T, Hkv, D, generator=g).to(torch.bfloat16).pin_memory()
+    hv = torch.randn(1, T, Hkv, D, generator=g).to(torch.bfloat16).pin_memory()
+    cu_dev = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    pipe = HostPrefill("cuda:0", chunk_tokens=256)
+    for causal in (True, False):
+        ho = torch.zeros(1, T, Hq, D, dtype=torch.bfloat16).pin_memory()
+        hl = torch.zeros(1, T, Hq, dtype=torch.float32).pin_memory()
+        pipe.run(hq, hk, hv, cu, ho, hl, scale=D ** -0.5, causal=causal)
+        torch.cuda.synchronize()
+        o, lse = ops.prefill(hq.cuda(), hk.cuda(), hv.cuda(), cu_seqlens=cu_dev, max_seqlen=max(lens),
+                             scale=D ** -0.5, causal=causal)
+        assert torch.equal(ho, o.cpu()) and torch.equal(hl, lse.cpu())
+    with pytest.raises(ValueError):
+        HostPrefill("cuda:0", chunk_tokens=100)

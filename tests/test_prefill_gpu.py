@@ -347,3 +347,30 @@ def test_sequence_longer_than_max_seqlen_is_cut_there():
     ref, rl = orc.dense_prefill_exact(q[:, :512], k[:, :512], v[:, :512], cu_cut, causal=False)
     assert maxabs(o[:, :512], ref) <= 5e-3
     assert maxabs(lse[:, :512], rl) <= 2e-3
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_row_ranges_equal_the_full_call(causal):
+    """b200attn_prefill_fwd_rows: query rows computed range by range equal the full call bit for
+    bit, rows outside the range are left alone, and a causal range reads no key at or beyond its
+    end (those rows hold NaN until their own range is computed)."""
+    from tritonops_b200 import ops
+    B, T, Hq, Hkv, D = 2, 1100, 4, 2, 128
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(B, T, Hq, D, generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn(B, T, Hkv, D, generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn(B, T, Hkv, D, generator=g).to(torch.bfloat16).cuda()
+    o_full, lse_full = ops.prefill(q, k, v, causal=causal)
+    o = torch.full_like(o_full, 7.0)
+    lse = torch.full_like(lse_full, 7.0)
+    kk, vv = (k.clone(), v.clone()) if causal else (k, v)
+    for r0, r1 in ((0, 256), (256, 768), (768, 1100)):
+        if causal:                         # keys that have "not arrived yet" are NaN
+            kk[:, r1:], vv[:, r1:] = float("nan"), float("nan")
+            kk[:, :r1], vv[:, :r1] = k[:, :r1], v[:, :r1]
+        ops.prefill_rows(q, kk, vv, o, lse, r0, r1, causal=causal)
+        assert torch.equal(o[:, r0:r1], o_full[:, r0:r1]) and torch.equal(lse[:, r0:r1], lse_full[:, r0:r1])
+        assert bool((o[:, r1:] == 7.0).all()) and bool((lse[:, r1:] == 7.0).all())
+    assert torch.equal(o, o_full) and torch.equal(lse, lse_full)
+    with pytest.raises(ValueError):
+        ops.prefill_rows(q, k, v, o, lse, 100, 512, causal=causal)

@@ -129,6 +129,7 @@ SYMBOLS = {
     "b200attn_strerror": (C.c_char_p, [C.c_int]),
     "b200attn_prefill_workspace_bytes": (C.c_size_t, [C.POINTER(PrefillArgs)]),
     "b200attn_prefill_fwd": (C.c_int, [C.POINTER(PrefillArgs), vp]),
+    "b200attn_prefill_fwd_rows": (C.c_int, [C.POINTER(PrefillArgs), C.c_int32, C.c_int32, vp]),
     "b200attn_sparse_prefill_fwd": (C.c_int, [C.POINTER(PrefillArgs), vp]),
     "b200attn_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeArgs)]),
     "b200attn_decode_fwd": (C.c_int, [C.POINTER(DecodeArgs), vp]),

@@ -157,6 +157,13 @@ int b200attn_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t st
   return prefill_fwd(args, false, (cudaStream_t)stream);
 }
 
+int b200attn_prefill_fwd_rows(const b200attn_prefill_args* args, int32_t row_begin, int32_t row_end,
+                              b200attn_stream_t stream) {
+  set_launch_count(0);
+  if (row_begin == 0 && row_end == 0x7fffffff) row_end -= 1;   // (that pair means "all rows" internally)
+  return prefill_fwd(args, false, (cudaStream_t)stream, row_begin, row_end);
+}
+
 int b200attn_sparse_prefill_fwd(const b200attn_prefill_args* args, b200attn_stream_t stream) {
   set_launch_count(0);
   return prefill_fwd(args, true, (cudaStream_t)stream);

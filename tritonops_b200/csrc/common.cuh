@@ -26,7 +26,8 @@ int device_info(const DeviceInfo** info);
 size_t decode_workspace_bytes(const b200attn_decode_args* a);
 int decode_fwd(const b200attn_decode_args* a, bool sparse, void* scratch, size_t scratch_bytes,
                cudaStream_t stream);
-int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream);
+// row_begin / row_end: the query rows of every sequence to compute (0, INT_MAX = all)
+int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream, int row_begin = 0, int row_end = 0x7fffffff);
 int decode_fwd_noalloc(const b200attn_decode_args* a, cudaStream_t stream);
 size_t prefill_bwd_workspace_bytes(const b200attn_prefill_bwd_args* a);
 int prefill_bwd(const b200attn_prefill_bwd_args* a, cudaStream_t stream);

@@ -21,6 +21,8 @@
 // S1 [128,256), O0 [256,256+D), O1 [384,384+D); P_t aliases the first half of S_t.
 // Every mbarrier wait is bounded; a timeout sets *status_word and the CTA drains.
 #include <mutex>
+#include <algorithm>
+#include <climits>
 #include <type_traits>
 
 #include "common.cuh"
@@ -56,6 +58,7 @@ struct PrefillParams {
   long long o_sb, o_st, o_sh, lse_sb, lse_st, lse_sh;
   int batch, heads_q, heads_kv, group, head_dim;
   int seqlen, n_pairs;
+  int pair_begin, pair_count;   // the 256-row query blocks this launch computes: [pair_begin, pair_begin + pair_count)
   int prefetch_ahead;   // CTAs resident at once: a CTA asks for the first tiles of CTA + this into L2
   int causal, window, win_local, win_global;
   float scale_log2;
@@ -212,11 +215,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   // first (longest-first keeps the tail of the launch short), and the group is
   // small enough that its K/V stay in L2 while its CTAs are resident.
   const int n_bh = p.batch * p.heads_q;
-  const int per_group = kHeadGroup * p.n_pairs;
+  const int per_group = kHeadGroup * p.pair_count;
   const int grp = blockIdx.x / per_group;
   const int in_grp = blockIdx.x - grp * per_group;
   const int g_heads = min(kHeadGroup, n_bh - grp * kHeadGroup);
-  const int pair = p.n_pairs - 1 - in_grp / g_heads;
+  const int pair = p.pair_begin + p.pair_count - 1 - in_grp / g_heads;
   const int bh = grp * kHeadGroup + in_grp % g_heads;
   const int h = bh % p.heads_q, b = bh / p.heads_q;
   const int hk = h / p.group;
@@ -369,7 +372,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           const int bi = blockIdx.x + p.prefetch_ahead;
           const int grp2 = bi / per_group, in2 = bi - grp2 * per_group;
           const int gh2 = min(kHeadGroup, n_bh - grp2 * kHeadGroup);
-          const int pair2 = p.n_pairs - 1 - in2 / gh2;
+          const int pair2 = p.pair_begin + p.pair_count - 1 - in2 / gh2;
           const int bh2 = grp2 * kHeadGroup + in2 % gh2;
           const int h2 = bh2 % p.heads_q, b2 = bh2 / p.heads_q;
           int ss2 = 0, len2 = p.seqlen, bc2 = b2;
@@ -824,7 +827,7 @@ static int launch_prefill(const b200attn_prefill_args* a, const PrefillParams& p
   // the shared-memory opt-in is per device: set on every call (a process may drive several GPUs)
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc) != cudaSuccess)
     return B200ATTN_ERR_CUDA;
-  const long long blocks = (long long)p.n_pairs * a->heads_q * a->batch;
+  const long long blocks = (long long)p.pair_count * a->heads_q * a->batch;
   if (blocks <= 0) return B200ATTN_OK;
   if (blocks > 0x7fffffffLL) return B200ATTN_ERR_TOO_LARGE;
   kern<<<(unsigned)blocks, kPrefillThreads, L::kAlloc, stream>>>(tq, tk, tv, p);
@@ -832,9 +835,14 @@ static int launch_prefill(const b200attn_prefill_args* a, const PrefillParams& p
   return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
 }
 
-int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream) {
+int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream, int row_begin, int row_end) {
   int st = validate_prefill(a, sparse);
   if (st != B200ATTN_OK) return st;
+  const bool all_rows = row_begin == 0 && row_end == INT_MAX;
+  if (!all_rows) {
+    if (sparse) return B200ATTN_ERR_MODE;
+    if (row_begin < 0 || row_end <= row_begin || row_begin % kPairM != 0) return B200ATTN_ERR_SHAPE;
+  }
   PrefillParams p;
   p.o = a->o; p.lse = a->lse; p.cu_seqlens = a->cu_seqlens;
   p.o_sb = a->o_stride_b; p.o_st = a->o_stride_t; p.o_sh = a->o_stride_h;
@@ -844,6 +852,11 @@ int prefill_fwd(const b200attn_prefill_args* a, bool sparse, cudaStream_t stream
   p.seqlen = a->seqlen;
   const int maxlen = a->cu_seqlens ? a->max_seqlen : a->seqlen;
   p.n_pairs = (maxlen + kPairM - 1) / kPairM;
+  // a row range ends on a 256-row boundary unless it runs to the end of the longest sequence
+  if (!all_rows && row_end < maxlen && row_end % kPairM != 0) return B200ATTN_ERR_SHAPE;
+  p.pair_begin = row_begin / kPairM;
+  p.pair_count = (int)std::min<long long>(p.n_pairs, ((long long)row_end + kPairM - 1) / kPairM) - p.pair_begin;
+  if (p.pair_count <= 0) return B200ATTN_OK;
   {
     const DeviceInfo* di = nullptr;
     st = device_info(&di);

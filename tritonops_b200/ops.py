@@ -309,6 +309,23 @@ def _prefill_op_impl(q: Tensor, k: Tensor, v: Tensor, cu_seqlens: Optional[Tenso
     Hkv = k.shape[2]
     o = torch.empty(Bt, T, Hq, v.shape[3], device=q.device, dtype=q.dtype)
     lse = torch.empty(Bt, T, Hq, device=q.device, dtype=torch.float32)
+    a = _prefill_args(q, k, v, o, lse, cu_seqlens, max_seqlen, scale, scale_has_log2e, causal, lse_base2,
+                      sparsity, window_local, window_global, block_idx, block_cnt, block_size)
+    L = _lib.lib()
+    fn = L.b200attn_prefill_fwd if sparsity == DENSE else L.b200attn_sparse_prefill_fwd
+    with torch.cuda.device(q.device):
+        _lib.check(fn(C.byref(a), _stream(q)))
+        _check_status(q.device, "the prefill forward")
+    _count()
+    return o, lse
+
+
+def _prefill_args(q, k, v, o, lse, cu_seqlens, max_seqlen, scale, scale_has_log2e, causal, lse_base2,
+                  sparsity=DENSE, window_local=0, window_global=0, block_idx=None, block_cnt=None,
+                  block_size=64) -> "PrefillArgs":
+    """b200attn_prefill_args for row-major tensors that have been checked by the caller."""
+    Bt, T, Hq, D = q.shape
+    Hkv = k.shape[2]
     a = PrefillArgs()
     a.q, a.k, a.v, a.o, a.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse)
     a.dtype, a.heads_q, a.heads_kv, a.head_dim = _DT[q.dtype], Hq, Hkv, D
@@ -332,13 +349,33 @@ def _prefill_op_impl(q: Tensor, k: Tensor, v: Tensor, cu_seqlens: Optional[Tenso
         a.n_qblocks, a.max_nnz = block_idx.shape[2], block_idx.shape[3]
     if DEBUG_STATUS:
         a.status_word = _ptr(_status_word(q.device))
+    return a
+
+
+def prefill_rows(q, k, v, o, lse, row_begin: int, row_end: int, *, scale=None, scale_has_log2e=False,
+                 causal=True, lse_base2=False) -> None:
+    """Dense prefill of the query rows [row_begin, row_end) only, written into the caller's
+    `o` [Bt, T, Hq, D] and `lse` fp32 [Bt, T, Hq]; see b200attn_prefill_fwd_rows in
+    include/b200attn.h.  q, k, v [Bt, T, H, D] with rows that are multiples of 8 elements apart;
+    with causal=True no K / V row at or beyond row_end is read."""
+    _same_head_dim(q, k, v, o)
+    _need_cuda(q, k, v, o, lse)
+    if q.dtype not in _DT or k.dtype != q.dtype or v.dtype != q.dtype or o.dtype != q.dtype:
+        raise ValueError("b200attn: q, k, v, o must share dtype float16 or bfloat16")
+    if lse.dtype != torch.float32 or tuple(lse.shape) != tuple(q.shape[:3]) or tuple(o.shape) != tuple(q.shape):
+        raise ValueError("b200attn: o must have q's shape and lse must be float32 [Bt, T, Hq]")
+    for t in (q, k, v, o):
+        if t.stride(3) != 1 or any(st % 8 for st in t.stride()[:3]):
+            raise ValueError("b200attn: prefill_rows takes row-major tensors with strides that are multiples of 8")
+    if scale is None:
+        scale, scale_has_log2e = q.shape[-1] ** -0.5, False
+    a = _prefill_args(q, k, v, o, lse, None, q.shape[1], float(scale), bool(scale_has_log2e), bool(causal),
+                      bool(lse_base2))
     L = _lib.lib()
-    fn = L.b200attn_prefill_fwd if sparsity == DENSE else L.b200attn_sparse_prefill_fwd
     with torch.cuda.device(q.device):
-        _lib.check(fn(C.byref(a), _stream(q)))
+        _lib.check(L.b200attn_prefill_fwd_rows(C.byref(a), int(row_begin), int(row_end), _stream(q)))
         _check_status(q.device, "the prefill forward")
     _count()
-    return o, lse
 
 
 _prefill_op = torch.library.custom_op("b200attn::prefill_fwd", _prefill_op_impl, mutates_args=())
