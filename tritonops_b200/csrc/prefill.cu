@@ -203,7 +203,8 @@ struct PrefillSmem {
 template <typename T, int DP, int BN, int NSTAGE, bool BLK>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-               const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
+               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+               const PrefillParams p) {
   using L = PrefillSmem<DP, BN, NSTAGE>;
   constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   constexpr uint32_t kIdescQK = idesc_f16(kFmt, false, kTileM, BN);
@@ -352,7 +353,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     if (warp == kLoadWarp) {
     // ================================================================= TMA
     {
-      if (elect_one()) { prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); }
+      if (elect_one()) { prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_o); }
       for (int t = 0; t < 2; ++t) {
         if (q0 + kTileM * t >= len) continue;
         if (elect_one()) {
@@ -679,10 +680,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         ++items;
       }
       // ------------------------------------------------------- epilogue
+      // A tile that lies wholly inside its sequence leaves as 16-bit through its dead Q buffer
+      // (same swizzled layout) and one copy-engine store per 64-column panel: written row by row
+      // from the threads, 16 bytes per lane at a stride of a token, the 32 KB of a tile keep the
+      // store path busy for thousands of cycles.  A tile that the sequence end cuts keeps the
+      // per-thread stores, which leave the next packed sequence's rows alone.
       const bool row_ok = qi < len;
+      const bool whole = q0t + kTileM <= len;
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const long long tok = (long long)seq_start + qi;
       T* orow = (T*)p.o + (p.cu_seqlens ? 0 : (long long)b * p.o_sb) + tok * p.o_st + (long long)h * p.o_sh;
+      uint8_t* sOut = smem_gen + t * L::kQBytes;       // every Q K^T product of this tile has completed
       if (items > 0) {
         mbar_wait(o_full(t), (items - 1) & 1, abort_flag);
         tc_fence_after();
@@ -697,16 +705,30 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 #pragma unroll
           for (int x = 0; x < 32; ++x) orr[x] = 0u;
         }
-        if (row_ok && 32 * cc < p.head_dim) {
 #pragma unroll
-          for (int x = 0; x < 32; x += 8) {
-            uint4 pk;
-            pk.x = pack2<T>(__uint_as_float(orr[x]) * inv, __uint_as_float(orr[x + 1]) * inv);
-            pk.y = pack2<T>(__uint_as_float(orr[x + 2]) * inv, __uint_as_float(orr[x + 3]) * inv);
-            pk.z = pack2<T>(__uint_as_float(orr[x + 4]) * inv, __uint_as_float(orr[x + 5]) * inv);
-            pk.w = pack2<T>(__uint_as_float(orr[x + 6]) * inv, __uint_as_float(orr[x + 7]) * inv);
+        for (int x = 0; x < 32; x += 8) {
+          uint4 pk;
+          pk.x = pack2<T>(__uint_as_float(orr[x]) * inv, __uint_as_float(orr[x + 1]) * inv);
+          pk.y = pack2<T>(__uint_as_float(orr[x + 2]) * inv, __uint_as_float(orr[x + 3]) * inv);
+          pk.z = pack2<T>(__uint_as_float(orr[x + 4]) * inv, __uint_as_float(orr[x + 5]) * inv);
+          pk.w = pack2<T>(__uint_as_float(orr[x + 6]) * inv, __uint_as_float(orr[x + 7]) * inv);
+          if (whole) {
+            const int col = 32 * cc + x;               // 16-byte chunk (col % 64) / 8 of panel col / 64
+            *reinterpret_cast<uint4*>(sOut + (col >> 6) * L::kQPanel + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4)) = pk;
+          } else if (row_ok && 32 * cc < p.head_dim) {
             *reinterpret_cast<uint4*>(orow + 32 * cc + x) = pk;
           }
+        }
+      }
+      if (whole) {
+        fence_proxy_async();
+        if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+        else asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (row == 0) {
+          for (int pn = 0; pn < kPanels; ++pn)
+            tma_store_4d(&tmap_o, sQ + t * L::kQBytes + pn * L::kQPanel, 64 * pn, seq_start + q0t, h, bcoord);
+          bulk_commit_group();
+          bulk_wait_read_all();
         }
       }
       if (row_ok && p.lse) {
@@ -807,10 +829,11 @@ static int launch_prefill(const b200attn_prefill_args* a, const PrefillParams& p
   using L = PrefillSmem<DP, BN, NSTAGE>;
   const long long tokens = a->cu_seqlens ? a->total_tokens : a->seqlen;
   const int tb = a->cu_seqlens ? 1 : a->batch;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   if (!make_tmap(&tq, a->dtype, a->q, a->head_dim, tokens, a->heads_q, tb, a->q_stride_t, a->q_stride_h, a->q_stride_b, kTileM) ||
       !make_tmap(&tk, a->dtype, a->k, a->head_dim, tokens, a->heads_kv, tb, a->k_stride_t, a->k_stride_h, a->k_stride_b, p.block_idx ? kBlk : BN) ||
-      !make_tmap(&tv, a->dtype, a->v, a->head_dim, tokens, a->heads_kv, tb, a->v_stride_t, a->v_stride_h, a->v_stride_b, p.block_idx ? kBlk : BN))
+      !make_tmap(&tv, a->dtype, a->v, a->head_dim, tokens, a->heads_kv, tb, a->v_stride_t, a->v_stride_h, a->v_stride_b, p.block_idx ? kBlk : BN) ||
+      !make_tmap(&to, a->dtype, a->o, a->head_dim, tokens, a->heads_q, tb, a->o_stride_t, a->o_stride_h, a->o_stride_b, kTileM))
     return B200ATTN_ERR_CUDA;
   auto kern = p.block_idx ? prefill_kernel<T, DP, BN, NSTAGE, true> : prefill_kernel<T, DP, BN, NSTAGE, false>;
   // the register count is a property of the binary: checked once per instantiation and mode
@@ -830,7 +853,7 @@ static int launch_prefill(const b200attn_prefill_args* a, const PrefillParams& p
   const long long blocks = (long long)p.pair_count * a->heads_q * a->batch;
   if (blocks <= 0) return B200ATTN_OK;
   if (blocks > 0x7fffffffLL) return B200ATTN_ERR_TOO_LARGE;
-  kern<<<(unsigned)blocks, kPrefillThreads, L::kAlloc, stream>>>(tq, tk, tv, p);
+  kern<<<(unsigned)blocks, kPrefillThreads, L::kAlloc, stream>>>(tq, tk, tv, to, p);
   set_launch_count(1);
   return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
 }
