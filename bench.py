@@ -43,7 +43,7 @@ LOG2E = 1.4426950408889634
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the named kernel and the ncu summary
 # the figure comes from (same workload unless the summary says it was scaled)
 TRAFFIC = {
-    "cfg2": (409.738496e6 + 119.315968e6, "profiles/prefill_cfg2_ncu.md"),
+    "cfg2": (412.162816e6 + 119.906816e6, "profiles/prefill_cfg2_ncu.md"),
     "cfg3": (1.301250e9 + 6.312448e6, "profiles/decode_cfg3_ncu.md"),
     "cfg2_backward": (824.896512e6 + 490.286848e6, "profiles/backward_cfg2_ncu.md"),
     "cfg4": (614.754816e6 + 124.699136e6, "profiles/sparse_prefill_cfg4_ncu.md"),
