@@ -188,9 +188,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
     // ============================================ loader warp: every load, and the dQ reduce-adds
     if (elect_one()) {
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
+      int n_q[2] = {0, 0}, n_do[2] = {0, 0};     // loads sent into each buffer so far
       auto load_do = [&](int it) {
         int i, hq;
         pair_of(it, i, hq);
+        ++n_do[it & 1];
         const uint32_t dst = sbase + ((it & 1) ? L::kDO1 : L::kDO), bar = bar_do0 + 8 * (it & 1);
         mbar_expect_tx(bar, L::kOperand);
         for (int pn = 0; pn < kPanels; ++pn)
@@ -199,6 +201,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       auto load_q = [&](int it) {
         int i, hq;
         pair_of(it, i, hq);
+        ++n_q[it & 1];
         const uint32_t dst = sbase + ((it & 1) ? L::kQ1 : L::kQ), bar = bar_q0 + 8 * (it & 1);
         mbar_expect_tx(bar, L::kOperand);
         for (int pn = 0; pn < kPanels; ++pn)
@@ -270,6 +273,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
         }
       }
       bulk_wait_all();
+      // after a wait gave up somewhere, loads may still be on their way into shared memory that
+      // nobody waits for any more: they must have landed before the CTA may exit
+      if (*abort_flag) {
+        mbar_drain(bar_kv, 0);
+        for (int bf = 0; bf < 2; ++bf) {
+          if (n_q[bf] > 0) mbar_drain(bar_q0 + 8 * bf, (n_q[bf] - 1) & 1);
+          if (n_do[bf] > 0) mbar_drain(bar_do0 + 8 * bf, (n_do[bf] - 1) & 1);
+        }
+      }
     }
     __syncwarp();
   } else if (warp == kBwdCtrlWarp) {
