@@ -354,8 +354,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     // ================================================================= TMA
     {
       if (elect_one()) { prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_o); }
-      for (int t = 0; t < 2; ++t) {
-        if (q0 + kTileM * t >= len) continue;
+      auto load_q = [&](int t) {
+        if (q0 + kTileM * t >= len) return;
         if (elect_one()) {
           mbar_expect_tx(q_full(t), L::kQBytes);
           for (int pn = 0; pn < kPanels; ++pn)
@@ -363,7 +363,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                         seq_start + q0 + kTileM * t, h, bcoord);
         }
         __syncwarp();
-      }
+      };
+      load_q(0);
       // The CTA that will start when one of the resident ones ends finds its Q tiles (read by
       // nobody else, so not in L2 yet) and its first K / V tile on the way: a CTA otherwise
       // spends ~2.5 us before its first product can start.  Issued behind this CTA's own
@@ -413,13 +414,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         ++cnt;
       };
       if (!blk) {
+        // the first product needs Q of tile 0 and the first K tile: those two first, then Q of tile 1
+        if (n_steps > 0) load_stage(&tmap_k, seq_start + seq.kv(0) * BN, 0, false);
+        load_q(1);
         for (int j = 0; j < n_steps; ++j) {
           const int row = seq_start + seq.kv(j) * BN;
-          load_stage(&tmap_k, row, 0, false);
+          if (j > 0) load_stage(&tmap_k, row, 0, false);
           load_stage(&tmap_v, row, 0, false);
           if (j == 1 || n_steps == 1) prefetch_next_cta();   // behind this CTA's own first loads
         }
       } else {
+        load_q(1);
         // per tile its own stream, in the order the MMA warp consumes the stages:
         // K(0,0) K(1,0), then per step V(0,j) K(0,j+1) V(1,j) K(1,j+1).  An odd
         // list repeats its last block in the second box (those columns are masked).
