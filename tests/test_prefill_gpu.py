@@ -349,6 +349,21 @@ def test_sequence_longer_than_max_seqlen_is_cut_there():
     assert maxabs(lse[:, :512], rl) <= 2e-3
 
 
+def test_row_ranges_gqa_half_precision_narrow_heads():
+    """The row-range call on a GQA shape with 64-wide heads in fp16, ranges of different sizes."""
+    from tritonops_b200 import ops
+    B, T, Hq, Hkv, D = 1, 1300, 8, 2, 64
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(B, T, Hq, D, generator=g).to(torch.float16).cuda()
+    k = torch.randn(B, T, Hkv, D, generator=g).to(torch.float16).cuda()
+    v = torch.randn(B, T, Hkv, D, generator=g).to(torch.float16).cuda()
+    o_full, lse_full = ops.prefill(q, k, v, causal=True)
+    o, lse = torch.zeros_like(o_full), torch.zeros_like(lse_full)
+    for r0, r1 in ((0, 1024), (1024, 1280), (1280, 1300)):
+        ops.prefill_rows(q, k, v, o, lse, r0, r1, causal=True)
+    assert torch.equal(o, o_full) and torch.equal(lse, lse_full)
+
+
 @pytest.mark.parametrize("causal", [True, False])
 def test_row_ranges_equal_the_full_call(causal):
     """b200attn_prefill_fwd_rows: query rows computed range by range equal the full call bit for
