@@ -408,6 +408,39 @@ def run_ours(args, rank, world, local_rank, cpu_base):
         windows.append(win)
         return reduce_max(ms), win
 
+    def graph_region(fn, steps, per_graph=10):
+        """The same steps replayed from a CUDA graph (10 calls per graph): what a decoding loop that
+        captures its launches sees.  A step of tens of microseconds is otherwise timed together with
+        the host's launch path.  None if the capture fails."""
+        try:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                fn()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for _ in range(per_graph):
+                        fn()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            ms, _ = region(g.replay, max(1, steps // per_graph))
+            return ms / per_graph
+        except Exception:
+            return None
+
+    def with_graph(entry, fn, steps, nbytes):
+        """Adds the graph-replayed time to a decoding entry and makes the better of the two the
+        entry's figure (both stay in the entry)."""
+        ms_g = graph_region(fn, steps)
+        entry["ms_per_step_eager"] = entry["ms_per_step"]
+        entry["ms_per_step_graph"] = ms_g
+        entry["timed_as"] = "eager launches"
+        if ms_g is not None and ms_g < entry["ms_per_step"]:
+            gb = nbytes / ms_g / 1e6
+            entry.update({"value": gb, "ms_per_step": ms_g, "achieved": gb / world, "frac": gb / world / pk["gbs"],
+                          "frac_of_nominal_8TBs": gb / world / 8000.0,
+                          "timed_as": "replayed from a CUDA graph of 10 steps"})
+        return entry
+
     # ---------------- headline: config 2, split by (sequence x KV head) units over the ranks
     c = CFG2
     S = c["S"]
@@ -540,6 +573,7 @@ def run_ours(args, rank, world, local_rank, cpu_base):
                  "algorithmic_bytes": w3.kv_bytes, **traffic("cfg3"),
                  "workload": "cfg3: GQA decode bf16 B=64 Hq=32 Hkv=8 D=128, cache 8192, len U[1024,8192] seed 2, "
                              "split chunks chosen by the library; 2.6 GB of KV per step, far larger than L2"}
+        with_graph(entry, f3, max(args.steps, 10), w3.kv_bytes)
         if world == 1:
             ms512, _ = region(lambda: ops.decode(q3, k3, v3, seqlens=sl3, max_seqlen=w3.max_seqlen, chunk=512),
                               max(args.steps, 10))
@@ -598,6 +632,7 @@ def run_ours(args, rank, world, local_rank, cpu_base):
                  "algorithmic_bytes": w5.kv_bytes, **traffic("cfg5"),
                  "workload": "cfg5: block-sparse decode bf16 B=32 H=32 D=128, KV 32768 = 512 blocks of 64, 64 blocks per "
                              "(b,h) seed 4"}
+        with_graph(entry, f5, max(args.steps, 10), w5.kv_bytes)
         if world == 1:
             entry["max_abs_err"] = err_block_decode(w5, f5(), [(0, 0), (5, 17), (13, 2), (31, 31), (20, 9), (8, 30)])
             entry["checked"] = "6 of 1024 (b, h) against fp32 math over the 64 gathered blocks on the device"
@@ -745,7 +780,9 @@ def run_ours(args, rank, world, local_rank, cpu_base):
         if "cfg2_backward_wrapper_ms" in ref_gpu and "ms_per_step" in rl.get("backward_cfg2", {}):
             ref_gpu["cfg2_backward_speedup"] = ref_gpu["cfg2_backward_wrapper_ms"] / rl["backward_cfg2"]["ms_per_step"]
         if "cfg3_wrapper_ms" in ref_gpu and "ms_per_step" in rl.get("decode_cfg3", {}):
-            ref_gpu["cfg3_speedup_wrapper"] = ref_gpu["cfg3_wrapper_ms"] / rl["decode_cfg3"]["ms_per_step"]
+            # (eager against eager: the reference wrapper is timed through its own Python launch path)
+            ref_gpu["cfg3_speedup_wrapper"] = ref_gpu["cfg3_wrapper_ms"] / rl["decode_cfg3"].get(
+                "ms_per_step_eager", rl["decode_cfg3"]["ms_per_step"])
         rl["reference_triton_gpu"] = ref_gpu
 
     if rank != 0:
