@@ -685,6 +685,7 @@ def run_ours(args, rank, world, local_rank, cpu_base):
                 "bit_identical_to_padded_decode": same,
                 "workload": "config 3's sequences in 64-key pages scattered at random over a pool, found through a "
                             "page table"}
+            with_graph(rl["paged_decode_cfg3"], fpg, max(args.steps, 10), w3.kv_bytes)
 
         guard("paged_decode_cfg3", do_paged)
 
