@@ -490,7 +490,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ C
       mbar_wait(bar_dq, it & 1, abort_flag);
       tc_fence_after();
       // scaled fp32 tile -> shared memory in the copy engine's 128-byte-swizzled layout
-      // (one panel per 32 columns); the control warp adds it to global memory
+      // (one panel per 32 columns); the loader warp adds it to global memory
       uint8_t* sStage = sgen + (half == 0 ? L::kDS : ((it & 1) ? L::kQ1 : L::kQ));
 #pragma unroll
       for (int c2 = 0; c2 < DP / 64; ++c2) {
