@@ -34,9 +34,9 @@ using namespace sm100;
 
 namespace {
 
-constexpr int kBwdComputeWarps = 8;   // warps 0-7: two threads per row (64 columns each)
-constexpr int kBwdCtrlWarp = kBwdComputeWarps;                // MMA issue, Q reloads, dQ reduce-adds
-constexpr int kBwdLoadWarp = kBwdComputeWarps + 1;            // K, V, dO loads
+constexpr int kBwdComputeWarps = 8;   // warps 0-7: two threads per key row (64 query columns each)
+constexpr int kBwdCtrlWarp = kBwdComputeWarps;                // issues the five products of every pair
+constexpr int kBwdLoadWarp = kBwdComputeWarps + 1;            // every load, and the dQ reduce-adds
 constexpr int kBwdThreads = 32 * (kBwdComputeWarps + 2);
 constexpr int kBwdComputeThreads = 32 * kBwdComputeWarps;
 constexpr int kT = 128;            // rows / keys per tile
