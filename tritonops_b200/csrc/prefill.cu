@@ -6,7 +6,7 @@
 // One CTA owns 256 consecutive query rows of one (sequence, query head) as two
 // 128-row tiles and walks the visible KV tiles once for both:
 //
-//   warp 9   TMA producer: Q tiles, then K_0, V_0, K_1, V_1, ... into a ring of
+//   warp 9   TMA producer: Q_0, K_0, Q_1, then V_0, K_1, V_1, ... into a ring of
 //            128-byte-swizzled shared-memory stages (mbarrier full/empty pairs)
 //   warp 8   MMA issuer (one thread): S_t = Q_t K_j^T and O_t += P_t V_j with
 //            tcgen05.mma; S, P and O live in tensor memory (TMEM)
@@ -14,7 +14,8 @@
 //            row reads its S row from TMEM, keeps the running max and sum in
 //            registers (base-2 exponentials), writes P back over S as packed
 //            16-bit values for the P V product, rescales O in TMEM only when
-//            the row max has grown by more than 2^8, and writes the output.
+//            the row max has grown by more than 2^8, and writes the output (a
+//            tile inside its sequence through the dead Q buffer and a TMA store).
 //
 // While one warpgroup computes the softmax of its tile the tensor core works on
 // the other tile, so MMA and exponentials overlap.  TMEM columns: S0 [0,128),
