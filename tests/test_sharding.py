@@ -119,3 +119,17 @@ def test_sharded_prefill_equals_unsharded_gloo():
         ret = mgr.dict()
         mp.spawn(_shard_worker, args=(world, 29537, ret), nprocs=world, join=True)
         assert ret[0] is True and ret[1] is True
+
+
+def test_host_pipeline_chunk_ranges():
+    """The row ranges the host pipeline streams a sequence in: they tile [0, n), start on
+    multiples of 256 and end on one or at n; a non-causal sequence is one range."""
+    from tritonops_b200.host import chunk_ranges
+    for n in (1, 255, 256, 257, 2048, 2049, 5000):
+        for chunk in (256, 1024, 2048):
+            r = chunk_ranges(n, chunk, True)
+            assert r[0][0] == 0 and r[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(r, r[1:]))
+            assert all(t0 % 256 == 0 and (t1 % 256 == 0 or t1 == n) and t1 > t0 for t0, t1 in r)
+        assert chunk_ranges(n, 1024, False) == [(0, n)]
+    assert chunk_ranges(0, 1024, True) == []

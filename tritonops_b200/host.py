@@ -21,6 +21,14 @@ from . import ops
 _ROW_ALIGN = 256      # b200attn_prefill_fwd_rows takes row ranges that start on a multiple of 256
 
 
+def chunk_ranges(n: int, chunk_tokens: int, causal: bool):
+    """Row ranges [t0, t1) in which a sequence of n tokens is streamed: every range starts on a
+    multiple of 256 and ends on one or at n, as b200attn_prefill_fwd_rows asks; a non-causal
+    sequence, whose queries need every key, is one range."""
+    step = chunk_tokens if causal else max(n, 1)
+    return [(t0, min(t0 + step, n)) for t0 in range(0, n, step)]
+
+
 class _Slot:
     def __init__(self):
         self.q = self.k = self.v = self.o = self.lse = None
@@ -94,10 +102,7 @@ class HostPrefill:
                 continue
             slot = self.slots[b % len(self.slots)]
             q, k, v, o, lse = slot.q[:, :n], slot.k[:, :n], slot.v[:, :n], slot.o[:, :n], slot.lse[:, :n]
-            # a non-causal query needs every key: one chunk
-            step = self.chunk if causal else n
-            for t0 in range(0, n, step):
-                t1 = min(t0 + step, n)
+            for t0, t1 in chunk_ranges(n, self.chunk, causal):
                 with torch.cuda.stream(self.s_in):
                     if t0 == 0 and slot.inputs_free is not None:
                         self.s_in.wait_event(slot.inputs_free)     # the slot's previous sequence has been attended to
